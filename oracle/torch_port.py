@@ -1,0 +1,127 @@
+"""The reference's CPU PyTorch decode path, restated.  TEST INFRASTRUCTURE ONLY.
+
+These are the functions the reference executes when no GPU backend applies;
+the benchmark times them on the host cores as the CPU baseline ("port"), and
+the tests use them as a second, float32 checker beside the C oracle.
+
+Parity status: pinned - compared with the reference's own functions on seeded
+inputs by ``tests/golden/make_golden.py`` (fixtures committed beside it).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def dense_decode(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+    """Exact decode as the reference's CPU path computes it.
+
+    Follows ``stream_attention/gate1.py:157-183`` (``dense_attention_forward``,
+    reached from ``decode.py:192-215`` for CPU tensors): BNHD inputs are
+    brought to head-major, KV heads are expanded to the query head count with
+    ``repeat_interleave`` and one non-causal SDPA call produces the result.
+    query [B,1,Hq,D], key/value [B,N,Hkv,D]; returns [B,1,Hq,D].
+    """
+
+    q = query.transpose(1, 2).contiguous()
+    k = key.transpose(1, 2).contiguous()
+    v = value.transpose(1, 2).contiguous()
+    q_heads, kv_heads = q.shape[1], k.shape[1]
+    if q_heads != kv_heads:
+        if q_heads % kv_heads:
+            raise ValueError("query heads must be a multiple of KV heads")
+        rep = q_heads // kv_heads
+        k = k.repeat_interleave(rep, dim=1)
+        v = v.repeat_interleave(rep, dim=1)
+    out = F.scaled_dot_product_attention(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False)
+    return out.transpose(1, 2).contiguous()
+
+
+def paged_decode(
+    query: torch.Tensor,
+    key_pages: torch.Tensor,
+    value_pages: torch.Tensor,
+    page_table: torch.Tensor,
+    lengths: torch.Tensor,
+    *,
+    layout: str = "NHD",
+) -> torch.Tensor:
+    """Page-streaming exact decode, one online-softmax update per page.
+
+    Follows ``stream_attention/paged.py:201-256`` (``paged_exact_reference``):
+    for every (row, query head) walk the row's active logical pages in order,
+    look the physical page up in ``page_table``, clip the last page to the
+    row length and fold the page into a running (max, denominator, numerator).
+    """
+
+    layout = layout.upper()
+    batch, _, heads, dim = (int(x) for x in query.shape)
+    if layout == "NHD":
+        page_size, kv_heads = int(key_pages.shape[1]), int(key_pages.shape[2])
+    else:
+        kv_heads, page_size = int(key_pages.shape[1]), int(key_pages.shape[2])
+    group = heads // kv_heads
+    scale = 1.0 / math.sqrt(float(dim))
+    out = torch.empty_like(query)
+    for b in range(batch):
+        n = int(lengths[b])
+        pages = -(-n // page_size)
+        for h in range(heads):
+            kvh = h // group
+            q = query[b, 0, h].float()
+            m = torch.tensor(float("-inf"))
+            den = torch.zeros(())
+            num = torch.zeros(dim)
+            for lp in range(pages):
+                pp = int(page_table[b, lp])
+                valid = min(page_size, n - lp * page_size)
+                if layout == "NHD":
+                    kp = key_pages[pp, :valid, kvh]
+                    vp = value_pages[pp, :valid, kvh]
+                else:
+                    kp = key_pages[pp, kvh, :valid]
+                    vp = value_pages[pp, kvh, :valid]
+                s = (kp.float() @ q) * scale
+                new_m = torch.maximum(m, s.max())
+                corr = torch.exp(m - new_m)
+                p = torch.exp(s - new_m)
+                num = num * corr + (p[:, None] * vp.float()).sum(dim=0)
+                den = den * corr + p.sum()
+                m = new_m
+            out[b, 0, h] = (num / den).to(out.dtype)
+    return out
+
+
+def seed_decode(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    tokens: torch.Tensor,
+) -> torch.Tensor:
+    """Seed-only decode: exact attention restricted to a fixed token set.
+
+    Follows ``benchmarks/profile_seed_only_route_bundle_decode.py:450-507``
+    (float32 scores, softmax and value accumulation over the gathered seed
+    tokens, GQA map ``kv_head = head // group``).  BNHD inputs as elsewhere in
+    this module: query [B,1,Hq,D], key/value [B,N,Hkv,D]; returns [B,1,Hq,D].
+    """
+
+    batch, _, heads, dim = (int(x) for x in query.shape)
+    kv_heads = int(key.shape[2])
+    group = heads // kv_heads
+    if tokens.numel() == 0:
+        return torch.zeros_like(query)
+    idx = tokens.to(torch.long)
+    k_sel = key.index_select(1, idx).float()      # [B,S,Hkv,D]
+    v_sel = value.index_select(1, idx).float()
+    kv_of_q = torch.arange(heads) // group
+    k_q = k_sel.index_select(2, kv_of_q)          # [B,S,Hq,D]
+    v_q = v_sel.index_select(2, kv_of_q)
+    q = query[:, 0].float()                       # [B,Hq,D]
+    scores = torch.einsum("bhd,bshd->bhs", q, k_q) / math.sqrt(float(dim))
+    probs = torch.softmax(scores, dim=-1)
+    out = torch.einsum("bhs,bshd->bhd", probs, v_q)
+    return out[:, None].to(query.dtype)
