@@ -1,0 +1,226 @@
+/*
+ * streamattn_b200 - C ABI of the B200 (sm_100a) decode-attention library.
+ *
+ * This is the drop-in boundary: plain pointers, sizes and a CUDA stream handle,
+ * no torch types.  Every entry point names the reference interface it replaces
+ * (paths inside the StreamAttn project).  All device pointers must belong to
+ * the device that is current on the calling thread; kernels are enqueued on
+ * `stream` and the calls return without synchronising.  Return value: SA_OK or
+ * an SA_ERR_* code; sa_last_error() then holds a message (thread-local).
+ *
+ * Tensors (D = head_dim contiguous in every tensor):
+ *   q        [batch, q_heads, D]        addressed by q_stride_b / q_stride_h (elements)
+ *   out      [batch, q_heads, D]        contiguous, same dtype as q      (SA_OUT_FINAL)
+ *            [batch, q_heads, D+2] f32  (o unnormalised, m, l)           (SA_OUT_STATE)
+ *            m is the running maximum of score*scale*log2(e) (base-2 domain),
+ *            l = sum 2^(s-m), o = sum 2^(s-m) v.
+ *   GQA map  kv_head = q_head / (q_heads / kv_heads)
+ *   scale    1/sqrt(D)
+ */
+#ifndef STREAMATTN_B200_H_
+#define STREAMATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SA_API __attribute__((visibility("default")))
+#else
+#define SA_API
+#endif
+
+typedef void *sa_stream_t; /* cudaStream_t */
+
+enum sa_status {
+    SA_OK = 0,
+    SA_ERR_INVALID = 1,     /* bad argument (maps to ValueError)                    */
+    SA_ERR_UNSUPPORTED = 2, /* valid but outside what the kernels cover             */
+    SA_ERR_CUDA = 3,        /* CUDA runtime / driver error (maps to RuntimeError)   */
+    SA_ERR_DEVICE = 4       /* no sm_100 device / driver entry point missing        */
+};
+
+enum sa_dtype { SA_DTYPE_BF16 = 0, SA_DTYPE_F16 = 1, SA_DTYPE_F32 = 2 };
+enum sa_index_dtype { SA_INDEX_I32 = 0, SA_INDEX_I64 = 1 };
+enum sa_page_layout { SA_LAYOUT_NHD = 0, SA_LAYOUT_HND = 1 };
+enum sa_block_order { SA_ORDER_SEQUENTIAL = 0, SA_ORDER_RECENT_FIRST = 1, SA_ORDER_SINK_RECENT_FIRST = 2 };
+enum sa_out_mode { SA_OUT_FINAL = 0, SA_OUT_STATE = 1 };
+enum sa_kernel_choice { SA_KERNEL_AUTO = 0, SA_KERNEL_STREAM = 1, SA_KERNEL_GENERIC = 2 };
+
+/* Bits of the device status word (sa_workspace_status). */
+enum sa_device_status {
+    SA_DEV_OK = 0,
+    SA_DEV_PIPELINE_TIMEOUT = 1, /* a bounded wait on a copy barrier gave up        */
+    SA_DEV_BAD_PAGE = 2          /* an active page_table entry was out of range and
+                                    was skipped (never dereferenced)                */
+};
+
+#define SA_MAX_SEED_BLOCKS 256
+
+/* Library / device queries. No reference counterpart beyond the capability
+ * gate torch.cuda.get_device_capability() == (9, 0) in
+ * stream_attention/backends/sm90/transposed_gqa_exact.py:254 and paged.py:320;
+ * here the gate is compute capability 10.x. */
+SA_API int sa_version(void);
+SA_API const char *sa_last_error(void);
+SA_API int sa_device_supported(int device);
+SA_API int sa_device_sm_count(int device);
+
+/* Workspace (fp32 split states + arrival counters + status word) every decode
+ * call needs.  Replaces the partial_o / partial_lse allocation of
+ * ExactDecodePlan.build (backends/sm90/transposed_gqa_exact.py:332-347) and
+ * make_paged_exact_workspace (kernels/paged_exact_triton.py:309-331).
+ * The buffer must be zero-filled ONCE before its first use; calls leave it
+ * ready for the next call.  Concurrent calls must not share a workspace.
+ * num_ctas: 0 = automatic.  Depends only on its arguments (no device query). */
+SA_API size_t sa_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim, int num_ctas);
+
+/* Synchronise `stream` and return the sa_device_status bits recorded by the
+ * kernels that used `workspace` (then clear them).  Negative on CUDA errors. */
+SA_API int sa_workspace_status(void *workspace, sa_stream_t stream);
+
+/*
+ * Exact contiguous GQA decode: out = softmax(q K^T / sqrt(D)) V over tokens
+ * [0, len_b) of each row, one query token per row, split-KV with an exact
+ * (m, l, o) merge fused into the same launch.
+ * Replaces exact_decode_out / exact_partial_out + exact_merge_warp_out
+ * (backends/sm90/transposed_gqa_exact_sources.py:100-132, 1003-1522) and
+ * exact_decode_attention_rows_triton_forward_out_bhnd
+ * (kernels/gate0_exact_refresh_triton.py:266-344).
+ * k/v: token n of kv head h of row b at  b*kv_stride_b + n*kv_stride_n + h*kv_stride_h
+ * (elements), which covers BNHD [B,N,Hkv,D] and head-major [B,Hkv,N,D].
+ * seq_lens: optional device array [batch] (lens_dtype) of valid token counts,
+ * clipped to kv_len (the reference's cache_position+1); NULL = kv_len.
+ */
+SA_API int sa_exact_decode(const void *q, const void *k, const void *v, void *out,
+                           void *workspace, size_t workspace_bytes,
+                           const void *seq_lens, int lens_dtype,
+                           int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                           int64_t q_stride_b, int64_t q_stride_h,
+                           int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                           int dtype, int out_mode, int num_ctas, int kernel_choice,
+                           sa_stream_t stream);
+
+/*
+ * Paged exact decode over a page pool with a page table and ragged per-row
+ * lengths.  Replaces paged_exact_decode_out, paged_fragmented_exact_decode_out,
+ * paged_fragmented_ragged_exact_decode_out
+ * (backends/sm90/transposed_gqa_exact_sources.py:116-132, 2082-2360) and
+ * paged_exact_decode_triton_forward_out (kernels/paged_exact_triton.py:193-306).
+ * k_pages/v_pages: NHD [num_pages, page_size, kv_heads, D] or
+ * HND [num_pages, kv_heads, page_size, D], contiguous.
+ * page_table [batch, max_pages_per_request] (table_dtype), -1 marks inactive
+ * trailing slots which are never read; seq_lens [batch] (lens_dtype).
+ * trace: optional device int32 [batch, max_pages_per_request]; when non-NULL
+ * the kernel records the physical page it loaded for every logical page it
+ * visited (other slots untouched) - the page-table walk, for parity checks.
+ */
+SA_API int sa_paged_decode(const void *q, const void *k_pages, const void *v_pages,
+                           const void *page_table, const void *seq_lens, void *out,
+                           void *workspace, size_t workspace_bytes, int32_t *trace,
+                           int batch, int q_heads, int kv_heads, int head_dim,
+                           int page_size, int max_pages_per_request, int64_t num_pages,
+                           int layout, int dtype, int table_dtype, int lens_dtype,
+                           int out_mode, int num_ctas, int kernel_choice, sa_stream_t stream);
+
+/*
+ * Seed block rule (host integer logic, no GPU needed).  Writes the seed blocks
+ * in the reference's order (sink, recent, middle; duplicates and out-of-range
+ * blocks dropped) and returns their count, or -1 if capacity is too small.
+ * Replaces policy_seed_blocks (seed_selectors.py:77-104), which equals the
+ * in-kernel rule of kernels/gate0_seed_only_triton.py:64-79.
+ */
+SA_API int sa_seed_blocks(int64_t kv_len, int block_size, int sink_blocks, int recent_blocks,
+                          int middle_seed_blocks, int block_order, int32_t *blocks_out, int capacity);
+
+/* Token set of a block list: block*bs + [0,bs) clipped to kv_len, deduplicated,
+ * ascending.  Returns the count or -1.  Replaces seed_token_indices_from_blocks
+ * (seed_selectors.py:152-173) / seed_indices (:107-133). */
+SA_API int64_t sa_seed_token_indices(int64_t kv_len, int block_size, const int32_t *blocks,
+                                     int num_blocks, int64_t *tokens_out, int64_t capacity);
+
+/*
+ * Seed-only decode: exact attention restricted to the seed token set, K/V shared
+ * by the query heads of a KV group (each seed token is read once per KV head).
+ * Replaces gate0_seed_only_attention_triton_forward_out[_prechecked]
+ * (kernels/gate0_seed_only_triton.py:30-127, 1458-1537, 2322-2378).
+ * sa_seed_decode derives the blocks from the policy parameters with
+ * sa_seed_blocks; sa_seed_decode_blocks takes an explicit HOST block list
+ * (<= SA_MAX_SEED_BLOCKS entries, any order, duplicates ignored).
+ */
+SA_API int sa_seed_decode(const void *q, const void *k, const void *v, void *out,
+                          void *workspace, size_t workspace_bytes,
+                          int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                          int64_t q_stride_b, int64_t q_stride_h,
+                          int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                          int dtype, int block_size, int sink_blocks, int recent_blocks,
+                          int middle_seed_blocks, int block_order,
+                          int num_ctas, int kernel_choice, sa_stream_t stream);
+
+SA_API int sa_seed_decode_blocks(const void *q, const void *k, const void *v, void *out,
+                                 void *workspace, size_t workspace_bytes,
+                                 int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                 int64_t q_stride_b, int64_t q_stride_h,
+                                 int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                 int dtype, int block_size, const int32_t *blocks_host, int num_blocks,
+                                 int num_ctas, int kernel_choice, sa_stream_t stream);
+
+/*
+ * Exact merge of split states: states [num_parts, rows, D+2] f32 (layout of
+ * SA_OUT_STATE) -> out [rows, D] in out_dtype.  Used after the cross-GPU
+ * gather of context-parallel decode.  Same arithmetic as
+ * _paged_exact_splitk_merge_kernel (kernels/paged_exact_triton.py:144-186)
+ * and exact_merge_warp_out (transposed_gqa_exact_sources.py:1460-1522).
+ */
+SA_API int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_dim,
+                           void *out, int out_dtype, sa_stream_t stream);
+
+/*
+ * Bound plans: validate once, keep the prepared launch (tensor maps, geometry),
+ * run many times with no per-call setup - what ExactDecodePlan.run /
+ * PagedExactDecodePlan.run do in the reference
+ * (transposed_gqa_exact.py:381-430, paged.py:490-538).  The create functions take
+ * the same arguments as the one-shot calls (without the stream) and return NULL
+ * on error.  A plan holds pointers, not ownership; the buffers must outlive it.
+ */
+typedef struct sa_plan sa_plan_t;
+
+SA_API sa_plan_t *sa_exact_plan_create(const void *q, const void *k, const void *v, void *out,
+                                       void *workspace, size_t workspace_bytes,
+                                       const void *seq_lens, int lens_dtype,
+                                       int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                       int64_t q_stride_b, int64_t q_stride_h,
+                                       int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                       int dtype, int out_mode, int num_ctas, int kernel_choice);
+
+SA_API sa_plan_t *sa_paged_plan_create(const void *q, const void *k_pages, const void *v_pages,
+                                       const void *page_table, const void *seq_lens, void *out,
+                                       void *workspace, size_t workspace_bytes, int32_t *trace,
+                                       int batch, int q_heads, int kv_heads, int head_dim,
+                                       int page_size, int max_pages_per_request, int64_t num_pages,
+                                       int layout, int dtype, int table_dtype, int lens_dtype,
+                                       int out_mode, int num_ctas, int kernel_choice);
+
+SA_API sa_plan_t *sa_seed_plan_create(const void *q, const void *k, const void *v, void *out,
+                                      void *workspace, size_t workspace_bytes,
+                                      int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                      int64_t q_stride_b, int64_t q_stride_h,
+                                      int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                      int dtype, int block_size, const int32_t *blocks_host, int num_blocks,
+                                      int num_ctas, int kernel_choice);
+
+SA_API int sa_plan_run(const sa_plan_t *plan, sa_stream_t stream);
+/* 1 = TMA/tensor-core streaming kernel, 2 = generic CUDA-core kernel. */
+SA_API int sa_plan_kernel(const sa_plan_t *plan);
+/* CTAs the plan launches and kernels enqueued per run. */
+SA_API int sa_plan_num_ctas(const sa_plan_t *plan);
+SA_API int sa_plan_launches(const sa_plan_t *plan);
+SA_API void sa_plan_destroy(sa_plan_t *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STREAMATTN_B200_H_ */

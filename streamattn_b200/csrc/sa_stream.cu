@@ -1,0 +1,693 @@
+// Streaming decode kernel for sm_100a: K/V tiles move HBM -> shared memory with
+// TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion,
+// no cluster multicast); every warp owns a private multi-stage ring of 16 KB
+// K+V tiles so the main loop has no cross-warp synchronisation.  QK^T and PV run
+// on the tensor cores (m16n8k16, query heads of one KV group on the M rows, fp32
+// accumulation) with a single-pass online softmax in the base-2 domain.
+//
+// Work is a flat list of tiles over all (row, kv head) pairs; CTA c takes the
+// contiguous slice [T*c/C, T*(c+1)/C), so ragged rows are balanced by tokens and
+// a pair may be covered by several CTAs.  Each covering CTA writes an (m, l, o)
+// state; the last one to arrive (atomic ticket, no waiting) merges them exactly
+// and writes the output, so one launch does producer and merge.
+//
+// The same kernel serves contiguous caches, paged caches (page-table lookup per
+// fragment) and seed-only decode (a short list of cache blocks).
+#include <mutex>
+
+#include "sa_stream.cuh"
+
+namespace sa {
+
+namespace {
+
+constexpr int kTileBytes = 8192;             // one K or one V tile
+constexpr int kStageBytes = 2 * kTileBytes;  // K + V
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct StreamParams {
+    const void *q;
+    int64_t q_sb, q_sh;
+    void *out;
+    int out_mode;
+    float *partials;
+    int *counters;
+    int *status;
+    int32_t *trace;
+    int batch, q_heads, kv_heads, group;
+    float scale_log2;
+    int frag_tokens;     // rows of one TMA box
+    int frags_per_tile;  // TILE_N / frag_tokens
+    int frags_per_unit;  // fragments per page / seed block (>= 1)
+    int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
+    int uniform_tiles;   // tiles per row when every row has the same length, else -1
+    SeqDesc seq;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up after kWaitLimitNs so a lost copy cannot hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ uint64_t make_evict_first_policy()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                                  uint32_t &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+template <typename T> struct Mma;
+template <> struct Mma<__nv_bfloat16> {
+    __device__ __forceinline__ static void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+            "{%0, %1, %2, %3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ __forceinline__ static uint32_t pack(float lo, float hi)
+    {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+template <> struct Mma<__half> {
+    __device__ __forceinline__ static void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+            "{%0, %1, %2, %3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ __forceinline__ static uint32_t pack(float lo, float hi)
+    {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+
+template <typename T, int D, int WARPS, int STAGES, bool ROWS16>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ StreamParams p)
+{
+    constexpr int TILE_N = kTileBytes / (D * 2);  // tokens per tile
+    constexpr int HALVES = D / 64;                // 128-byte column groups per row
+    constexpr int HALF_BYTES = TILE_N * 128;
+    constexpr int NT_S = TILE_N / 8;   // score n-tiles (8 tokens each)
+    constexpr int KS_QK = D / 16;      // k-steps of q.k
+    constexpr int NT_O = D / 8;        // output n-tiles (8 columns each)
+    constexpr int KS_PV = TILE_N / 16; // k-steps of p.v
+    constexpr int STATE_STRIDE = D + 2;
+    constexpr int NTHREADS = WARPS * 32;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + WARPS * STAGES * kStageBytes);
+    int *prefix = reinterpret_cast<int *>(bars + WARPS * STAGES);
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int g = lane >> 2;
+    const int t4 = lane & 3;
+    const int C = gridDim.x;
+    const int c = blockIdx.x;
+    const int group = p.group;
+    const bool ragged = p.uniform_tiles < 0;
+
+    const uint32_t ring_u32 = smem_u32(ring) + warp * STAGES * kStageBytes;
+    const uint32_t bar_u32 = smem_u32(bars) + warp * STAGES * 8;
+    uint8_t *warp_ring = ring + warp * STAGES * kStageBytes;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (ragged && warp == 0) {
+        int running = 0;
+        for (int base = 0; base < p.batch; base += 32) {
+            const int b = base + lane;
+            int x = 0;
+            if (b < p.batch) x = static_cast<int>((row_vlen(p.seq, b) + TILE_N - 1) / TILE_N);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, x, o);
+                if (lane >= o) x += y;
+            }
+            if (b < p.batch) prefix[b + 1] = running + x;
+            running += __shfl_sync(0xffffffffu, x, 31);
+        }
+        if (lane == 0) prefix[0] = 0;
+    }
+    fence_proxy_async();
+    __syncthreads();
+
+    const uint64_t policy = make_evict_first_policy();
+    const int Hkv = p.kv_heads;
+    auto tiles_before = [&](int b) -> int64_t {
+        return ragged ? static_cast<int64_t>(prefix[b]) : static_cast<int64_t>(b) * p.uniform_tiles;
+    };
+    const int64_t total_tiles = static_cast<int64_t>(Hkv) * tiles_before(p.batch);
+    auto owner = [&](int64_t x) -> int64_t { return ((x + 1) * C - 1) / total_tiles; };
+
+    // Rows with no tokens are not part of the tile list: write their (empty) result here.
+    for (int b = c; b < p.batch; b += C) {
+        if (tiles_before(b + 1) != tiles_before(b)) continue;
+        for (int i = tid; i < p.q_heads * D; i += NTHREADS) {
+            const int h = i / D, d = i % D;
+            if (p.out_mode == SA_OUT_FINAL)
+                static_cast<T *>(p.out)[(static_cast<int64_t>(b) * p.q_heads + h) * D + d] = Elem<T>::from_float(0.0f);
+            else
+                static_cast<float *>(p.out)[(static_cast<int64_t>(b) * p.q_heads + h) * STATE_STRIDE + d] = 0.0f;
+        }
+        if (p.out_mode != SA_OUT_FINAL) {
+            for (int h = tid; h < p.q_heads; h += NTHREADS) {
+                float *st = static_cast<float *>(p.out) + (static_cast<int64_t>(b) * p.q_heads + h) * STATE_STRIDE;
+                st[D] = -INFINITY;
+                st[D + 1] = 0.0f;
+            }
+        }
+    }
+
+    if (total_tiles == 0) return;
+    const int64_t lo = total_tiles * c / C;
+    const int64_t hi = total_tiles * (c + 1) / C;
+    int64_t cur = lo;
+    uint32_t tile_base = 0;  // tiles this warp has pushed through its ring so far
+    bool dead = false;       // a bounded wait gave up: stop computing, keep the barriers
+
+    while (cur < hi) {
+        // Locate the (row, kv head) pair that owns global tile `cur`.
+        int b;
+        if (ragged) {
+            int lo_b = 0, hi_b = p.batch;  // largest b with Hkv*prefix[b] <= cur
+            while (hi_b - lo_b > 1) {
+                const int mid = (lo_b + hi_b) >> 1;
+                if (static_cast<int64_t>(Hkv) * prefix[mid] <= cur) lo_b = mid; else hi_b = mid;
+            }
+            b = lo_b;
+        } else {
+            b = static_cast<int>(cur / (static_cast<int64_t>(Hkv) * p.uniform_tiles));
+        }
+        const int row_tiles = static_cast<int>(tiles_before(b + 1) - tiles_before(b));
+        const int64_t row_start = static_cast<int64_t>(Hkv) * tiles_before(b);
+        const int kvh = static_cast<int>((cur - row_start) / row_tiles);
+        const int64_t pair_start = row_start + static_cast<int64_t>(kvh) * row_tiles;
+        const int64_t pair_end = pair_start + row_tiles;
+        const int seg_lo = static_cast<int>(cur - pair_start);
+        const int seg_hi = static_cast<int>((hi < pair_end ? hi : pair_end) - pair_start);
+        const int pair = b * Hkv + kvh;
+        const int64_t vlen = row_vlen(p.seq, b);
+
+        // Query fragments of this KV group (A operand of q.k), rows >= group are zero.
+        uint32_t qa[KS_QK][4];
+        {
+            const T *qrow0 = static_cast<const T *>(p.q) + b * p.q_sb + (static_cast<int64_t>(kvh) * group + g) * p.q_sh;
+            const T *qrow1 = qrow0 + 8 * p.q_sh;
+            const bool ok0 = g < group;
+            const bool ok1 = ROWS16 && (g + 8 < group);
+#pragma unroll
+            for (int ks = 0; ks < KS_QK; ++ks) {
+                const int col = ks * 16 + 2 * t4;
+                qa[ks][0] = ok0 ? *reinterpret_cast<const uint32_t *>(qrow0 + col) : 0u;
+                qa[ks][1] = ok1 ? *reinterpret_cast<const uint32_t *>(qrow1 + col) : 0u;
+                qa[ks][2] = ok0 ? *reinterpret_cast<const uint32_t *>(qrow0 + col + 8) : 0u;
+                qa[ks][3] = ok1 ? *reinterpret_cast<const uint32_t *>(qrow1 + col + 8) : 0u;
+            }
+        }
+
+        const int seg_tiles = seg_hi - seg_lo;
+        const int n_w = seg_tiles > warp ? (seg_tiles - warp + WARPS - 1) / WARPS : 0;
+
+        // Issue the TMA copies of this warp's j-th tile of the segment.
+        auto issue = [&](int j) {
+            const int lt = seg_lo + warp + j * WARPS;
+            const uint32_t slot = (tile_base + j) % STAGES;
+            const uint32_t stage = ring_u32 + slot * kStageBytes;
+            const uint32_t bar = bar_u32 + slot * 8;
+            bool valid = false;
+            int tok = 0, outer = 0;
+            if (lane < p.frags_per_tile) {
+                const int64_t vfrag = static_cast<int64_t>(lt) * p.frags_per_tile + lane;
+                const int64_t vtok0 = vfrag * p.frag_tokens;
+                valid = vtok0 < vlen;
+                if (valid) {
+                    if (p.seq.mode == kContig) {
+                        tok = static_cast<int>(vtok0);
+                        outer = b;
+                    } else if (p.seq.mode == kPaged) {
+                        const int64_t lp = vfrag / p.frags_per_unit;
+                        const int sub = static_cast<int>(vfrag % p.frags_per_unit);
+                        const int64_t page =
+                            load_index(p.seq.page_table, p.seq.table_i64, static_cast<int64_t>(b) * p.seq.max_pages + lp);
+                        if (page < 0 || page >= p.seq.num_pages) {
+                            valid = false;
+                            atomicOr(p.status, SA_DEV_BAD_PAGE);
+                        } else {
+                            tok = sub * p.frag_tokens;
+                            outer = static_cast<int>(page);
+                            if (p.trace != nullptr && kvh == 0 && sub == 0)
+                                p.trace[static_cast<int64_t>(b) * p.seq.max_pages + lp] = static_cast<int32_t>(page);
+                        }
+                    } else {
+                        const int blk = p.seq.blocks[vfrag / p.frags_per_unit];
+                        const int sub = static_cast<int>(vfrag % p.frags_per_unit);
+                        tok = blk * p.seq.block_size + sub * p.frag_tokens;
+                        outer = b;
+                    }
+                }
+            }
+            const unsigned mask = __ballot_sync(0xffffffffu, valid);
+            if (lane == 0)
+                mbar_arrive_expect_tx(bar, static_cast<uint32_t>(__popc(mask)) * p.frag_tokens * 128 * HALVES * 2);
+            __syncwarp();
+            if (valid) {
+                const uint32_t dst = stage + lane * p.frag_tokens * 128;
+                const int c1 = p.tok_dim == 1 ? tok : kvh;
+                const int c2 = p.tok_dim == 1 ? kvh : tok;
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf) {
+                    tma_load_4d(dst + hf * HALF_BYTES, &tm_k, bar, hf * 64, c1, c2, outer, policy);
+                    tma_load_4d(dst + kTileBytes + hf * HALF_BYTES, &tm_v, bar, hf * 64, c1, c2, outer, policy);
+                }
+            }
+        };
+
+        const int prologue = n_w < STAGES ? n_w : STAGES;
+        for (int j = 0; j < prologue; ++j) issue(j);
+
+        float m_run[2] = {-INFINITY, -INFINITY};
+        float l_run[2] = {0.0f, 0.0f};
+        float o_acc[NT_O][4];
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+            o_acc[i][0] = 0.0f;
+            o_acc[i][1] = 0.0f;
+            o_acc[i][2] = 0.0f;
+            o_acc[i][3] = 0.0f;
+        }
+
+        for (int j = 0; j < n_w; ++j) {
+            const int lt = seg_lo + warp + j * WARPS;
+            const uint32_t slot = (tile_base + j) % STAGES;
+            const uint32_t parity = ((tile_base + j) / STAGES) & 1u;
+            const uint32_t kb = ring_u32 + slot * kStageBytes;
+            const uint32_t vb = kb + kTileBytes;
+            if (!dead && !mbar_wait(bar_u32 + slot * 8, parity)) {
+                dead = true;
+                atomicOr(p.status, SA_DEV_PIPELINE_TIMEOUT);
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            if (dead) continue;
+
+            const int64_t tile_tok0 = static_cast<int64_t>(lt) * TILE_N;
+            const int n_valid = vlen - tile_tok0 < TILE_N ? static_cast<int>(vlen - tile_tok0) : TILE_N;
+            const bool tail = n_valid < TILE_N;
+
+            // scores: S[16 rows = heads, TILE_N tokens] = Q K^T
+            float s_acc[NT_S][4];
+#pragma unroll
+            for (int nt = 0; nt < NT_S; ++nt) {
+                s_acc[nt][0] = 0.0f;
+                s_acc[nt][1] = 0.0f;
+                s_acc[nt][2] = 0.0f;
+                s_acc[nt][3] = 0.0f;
+#pragma unroll
+                for (int kk = 0; kk < KS_QK / 2; ++kk) {
+                    const int chunk = kk * 4 + (lane >> 3);
+                    const int row = nt * 8 + (lane & 7);
+                    const uint32_t addr =
+                        kb + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4(addr, r0, r1, r2, r3);
+                    Mma<T>::run(s_acc[nt], qa[2 * kk], r0, r1);
+                    Mma<T>::run(s_acc[nt], qa[2 * kk + 1], r2, r3);
+                }
+            }
+
+            if (tail) {
+                // Mask tokens past the row length and clear their V rows so that stale or
+                // never-written shared memory cannot reach the accumulators.
+#pragma unroll
+                for (int nt = 0; nt < NT_S; ++nt) {
+                    const int col = nt * 8 + 2 * t4;
+                    if (col >= n_valid) {
+                        s_acc[nt][0] = -INFINITY;
+                        s_acc[nt][2] = -INFINITY;
+                    }
+                    if (col + 1 >= n_valid) {
+                        s_acc[nt][1] = -INFINITY;
+                        s_acc[nt][3] = -INFINITY;
+                    }
+                }
+                uint8_t *vtile = warp_ring + slot * kStageBytes + kTileBytes;
+                const int chunks = (TILE_N - n_valid) * 8;
+                for (int hf = 0; hf < HALVES; ++hf)
+                    for (int i = lane; i < chunks; i += 32)
+                        *reinterpret_cast<uint4 *>(vtile + hf * HALF_BYTES + n_valid * 128 + i * 16) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                __syncwarp();
+            }
+
+            // online softmax (base-2 domain), rows g and (ROWS16) g+8
+            uint32_t pa[KS_PV][4];
+            {
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < NT_S; ++nt) {
+                    mx0 = fmaxf(mx0, fmaxf(s_acc[nt][0], s_acc[nt][1]));
+                    if (ROWS16) mx1 = fmaxf(mx1, fmaxf(s_acc[nt][2], s_acc[nt][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                if (ROWS16) {
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                }
+                const float m_new0 = fmaxf(m_run[0], mx0 * p.scale_log2);
+                const float alpha0 = exp2_diff(m_run[0], m_new0);
+                const float neg_m0 = m_new0 == -INFINITY ? 0.0f : -m_new0;
+                float m_new1 = -INFINITY, alpha1 = 0.0f, neg_m1 = 0.0f;
+                if (ROWS16) {
+                    m_new1 = fmaxf(m_run[1], mx1 * p.scale_log2);
+                    alpha1 = exp2_diff(m_run[1], m_new1);
+                    neg_m1 = m_new1 == -INFINITY ? 0.0f : -m_new1;
+                }
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < NT_S; ++nt) {
+                    const float p0 = exp2f(fmaf(s_acc[nt][0], p.scale_log2, neg_m0));
+                    const float p1 = exp2f(fmaf(s_acc[nt][1], p.scale_log2, neg_m0));
+                    sum0 += p0 + p1;
+                    float p2 = 0.0f, p3 = 0.0f;
+                    if (ROWS16) {
+                        p2 = exp2f(fmaf(s_acc[nt][2], p.scale_log2, neg_m1));
+                        p3 = exp2f(fmaf(s_acc[nt][3], p.scale_log2, neg_m1));
+                        sum1 += p2 + p3;
+                    }
+                    const int kt = nt >> 1;
+                    const int hi_half = (nt & 1) * 2;
+                    pa[kt][hi_half] = Mma<T>::pack(p0, p1);
+                    pa[kt][hi_half + 1] = ROWS16 ? Mma<T>::pack(p2, p3) : 0u;
+                }
+                l_run[0] = l_run[0] * alpha0 + sum0;
+                m_run[0] = m_new0;
+                if (ROWS16) {
+                    l_run[1] = l_run[1] * alpha1 + sum1;
+                    m_run[1] = m_new1;
+                }
+#pragma unroll
+                for (int i = 0; i < NT_O; ++i) {
+                    o_acc[i][0] *= alpha0;
+                    o_acc[i][1] *= alpha0;
+                    if (ROWS16) {
+                        o_acc[i][2] *= alpha1;
+                        o_acc[i][3] *= alpha1;
+                    }
+                }
+            }
+
+            // O[16 rows, D] += P V
+#pragma unroll
+            for (int kt = 0; kt < KS_PV; ++kt) {
+#pragma unroll
+                for (int dp = 0; dp < NT_O / 2; ++dp) {
+                    const int row = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int chunk = dp * 2 + (lane >> 4);
+                    const uint32_t addr =
+                        vb + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4_trans(addr, r0, r1, r2, r3);
+                    Mma<T>::run(o_acc[2 * dp], pa[kt], r0, r1);
+                    Mma<T>::run(o_acc[2 * dp + 1], pa[kt], r2, r3);
+                }
+            }
+
+            // Order this warp's shared-memory accesses before the async-proxy writes of the refill.
+            fence_proxy_async();
+            __syncwarp();
+            if (j + STAGES < n_w) issue(j + STAGES);
+        }
+        tile_base += n_w;
+
+        // Warp state -> this warp's (now idle) ring memory: [ROWS][D+2] floats = (o, m, l).
+        {
+            l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+            l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+            if (ROWS16) {
+                l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+                l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+            }
+            float *area = reinterpret_cast<float *>(warp_ring);
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i) {
+                const int d = i * 8 + 2 * t4;
+                *reinterpret_cast<float2 *>(area + g * STATE_STRIDE + d) = make_float2(o_acc[i][0], o_acc[i][1]);
+                if (ROWS16)
+                    *reinterpret_cast<float2 *>(area + (g + 8) * STATE_STRIDE + d) =
+                        make_float2(o_acc[i][2], o_acc[i][3]);
+            }
+            if (t4 == 0) {
+                area[g * STATE_STRIDE + D] = m_run[0];
+                area[g * STATE_STRIDE + D + 1] = l_run[0];
+                if (ROWS16) {
+                    area[(g + 8) * STATE_STRIDE + D] = m_run[1];
+                    area[(g + 8) * STATE_STRIDE + D + 1] = l_run[1];
+                }
+            }
+        }
+        __syncthreads();
+
+        // Combine the warps of this CTA, then either finish the pair or publish a state.
+        const int64_t first_cta = owner(pair_start);
+        const int nseg = static_cast<int>(owner(pair_end - 1) - first_cta) + 1;
+        const int64_t slot_stride = static_cast<int64_t>(group) * STATE_STRIDE;
+        float *my_slot = p.partials + (static_cast<int64_t>(c) + pair) * slot_stride;
+        const int64_t out_row0 = static_cast<int64_t>(b) * p.q_heads + static_cast<int64_t>(kvh) * group;
+        for (int idx = tid; idx < group * D; idx += NTHREADS) {
+            const int row = idx / D;
+            const int d = idx - row * D;
+            float big = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float *area = reinterpret_cast<const float *>(ring + w * STAGES * kStageBytes);
+                big = fmaxf(big, area[row * STATE_STRIDE + D]);
+            }
+            float acc = 0.0f, total_l = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float *area = reinterpret_cast<const float *>(ring + w * STAGES * kStageBytes);
+                const float wgt = exp2_diff(area[row * STATE_STRIDE + D], big);
+                acc += wgt * area[row * STATE_STRIDE + d];
+                total_l += wgt * area[row * STATE_STRIDE + D + 1];
+            }
+            if (nseg == 1 && p.out_mode == SA_OUT_FINAL) {
+                static_cast<T *>(p.out)[(out_row0 + row) * D + d] =
+                    Elem<T>::from_float(total_l > 0.0f ? acc / total_l : 0.0f);
+            } else {
+                float *dst = nseg == 1 ? static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE
+                                       : my_slot + row * STATE_STRIDE;
+                dst[d] = acc;
+                if (d == 0) {
+                    dst[D] = big;
+                    dst[D + 1] = total_l;
+                }
+            }
+        }
+
+        if (nseg > 1) {
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_last = atomicAdd(p.counters + pair, 1) == nseg - 1;
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const float *first_slot = p.partials + (first_cta + pair) * slot_stride;
+                for (int idx = tid; idx < group * D; idx += NTHREADS) {
+                    const int row = idx / D;
+                    const int d = idx - row * D;
+                    float big = -INFINITY;
+                    for (int i = 0; i < nseg; ++i)
+                        big = fmaxf(big, __ldcg(first_slot + i * slot_stride + row * STATE_STRIDE + D));
+                    float acc = 0.0f, total_l = 0.0f;
+                    for (int i = 0; i < nseg; ++i) {
+                        const float *st = first_slot + i * slot_stride + row * STATE_STRIDE;
+                        const float wgt = exp2_diff(__ldcg(st + D), big);
+                        acc += wgt * __ldcg(st + d);
+                        total_l += wgt * __ldcg(st + D + 1);
+                    }
+                    if (p.out_mode == SA_OUT_FINAL) {
+                        static_cast<T *>(p.out)[(out_row0 + row) * D + d] =
+                            Elem<T>::from_float(total_l > 0.0f ? acc / total_l : 0.0f);
+                    } else {
+                        float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
+                        dst[d] = acc;
+                        if (d == 0) {
+                            dst[D] = big;
+                            dst[D + 1] = total_l;
+                        }
+                    }
+                }
+                if (tid == 0) p.counters[pair] = 0;  // ready for the next launch
+            }
+        }
+        fence_proxy_async();
+        __syncthreads();  // ring memory and s_last are reused by the next segment
+        cur = pair_start + seg_hi;
+    }
+}
+
+struct KernelEntry {
+    const void *fn;
+    size_t smem;
+};
+
+template <typename T, int D, int WARPS, int STAGES, bool ROWS16>
+cudaError_t launch_instance(const CUtensorMap &mk, const CUtensorMap &mv, const StreamParams &sp, int ctas,
+                            int batch, cudaStream_t stream)
+{
+    auto kernel = stream_decode_kernel<T, D, WARPS, STAGES, ROWS16>;
+    const size_t smem = 1024 + static_cast<size_t>(WARPS) * STAGES * kStageBytes + WARPS * STAGES * 8 +
+                        (static_cast<size_t>(batch) + 1) * 4 + 16;
+    // Opt in to the dynamic shared memory this launch needs (grows only; per device).
+    static std::mutex mu;
+    static size_t configured[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (configured[dev] < smem) {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (err != cudaSuccess) return err;
+            configured[dev] = smem;
+        }
+    }
+    kernel<<<ctas, WARPS * 32, smem, stream>>>(mk, mv, sp);
+    return cudaGetLastError();
+}
+
+template <typename T, int D>
+cudaError_t launch_dim(const CUtensorMap &mk, const CUtensorMap &mv, const StreamParams &sp, int ctas, int batch,
+                       bool rows16, cudaStream_t stream)
+{
+    if (rows16) return launch_instance<T, D, kStreamWarps, kStreamStages, true>(mk, mv, sp, ctas, batch, stream);
+    return launch_instance<T, D, kStreamWarps, kStreamStages, false>(mk, mv, sp, ctas, batch, stream);
+}
+
+}  // namespace
+
+int stream_tile_tokens(int head_dim) { return kTileBytes / (head_dim * 2); }
+
+cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream)
+{
+    StreamParams sp;
+    sp.q = p.q;
+    sp.q_sb = p.q_sb;
+    sp.q_sh = p.q_sh;
+    sp.out = p.out;
+    sp.out_mode = p.out_mode;
+    sp.partials = p.ws.partials;
+    sp.counters = p.ws.counters;
+    sp.status = p.ws.status;
+    sp.trace = p.trace;
+    sp.batch = p.batch;
+    sp.q_heads = p.q_heads;
+    sp.kv_heads = p.kv_heads;
+    sp.group = p.q_heads / p.kv_heads;
+    sp.scale_log2 = kLog2e / sqrtf(static_cast<float>(p.head_dim));
+    sp.frag_tokens = geo.frag_tokens;
+    sp.frags_per_tile = geo.frags_per_tile;
+    sp.frags_per_unit = geo.frags_per_unit;
+    sp.tok_dim = geo.tok_dim;
+    sp.uniform_tiles = geo.uniform_tiles;
+    sp.seq = p.seq;
+    const bool rows16 = sp.group > 8;
+    if (p.dtype == SA_DTYPE_BF16) {
+        if (p.head_dim == 64)
+            return launch_dim<__nv_bfloat16, 64>(geo.map_k, geo.map_v, sp, geo.num_ctas, p.batch, rows16, stream);
+        return launch_dim<__nv_bfloat16, 128>(geo.map_k, geo.map_v, sp, geo.num_ctas, p.batch, rows16, stream);
+    }
+    if (p.head_dim == 64)
+        return launch_dim<__half, 64>(geo.map_k, geo.map_v, sp, geo.num_ctas, p.batch, rows16, stream);
+    return launch_dim<__half, 128>(geo.map_k, geo.map_v, sp, geo.num_ctas, p.batch, rows16, stream);
+}
+
+}  // namespace sa

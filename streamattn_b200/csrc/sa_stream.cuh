@@ -1,0 +1,25 @@
+// Host-side description of one launch of the streaming (TMA + tensor core) kernel.
+#pragma once
+
+#include "sa_common.cuh"
+
+namespace sa {
+
+constexpr int kStreamWarps = 4;
+constexpr int kStreamStages = 3;
+
+struct StreamGeometry {
+    CUtensorMap map_k;
+    CUtensorMap map_v;
+    int frag_tokens;     // rows of one TMA box
+    int frags_per_tile;  // boxes per 8 KB tile
+    int frags_per_unit;  // boxes per page / seed block
+    int tok_dim;         // TMA coordinate carrying the token index (1 or 2)
+    int uniform_tiles;   // tiles per row if all rows are equally long, else -1
+    int num_ctas;
+};
+
+int stream_tile_tokens(int head_dim);
+cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream);
+
+}  // namespace sa

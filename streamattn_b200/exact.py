@@ -1,0 +1,130 @@
+"""Bound exact-decode plan on the sm_100a kernels.
+
+Counterpart of the reference's ``ExactDecodePlan``
+(``stream_attention/backends/sm90/transposed_gqa_exact.py:264-430``): built once
+over stable Q/K/V/output buffers, ``run()`` enqueues one launch and allocates
+nothing.  Where the reference runs a producer kernel plus a merge kernel over a
+fixed split count, this plan runs one launch whose CTAs take equal slices of a
+flat tile list and merge their split states in the same launch; ``num_splits``
+is kept as the knob "CTAs per (row, KV head)".
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import native
+from .decode import infer_kv_layout
+
+SM100_EXACT_BACKEND = "sm100_gqa_exact"
+
+
+def choose_num_splits(*, batch: int, kv_heads: int, kv_len: int, target_producer_ctas: int = 256) -> int:
+    """Smallest split count reaching the CTA target (reference transposed_gqa_exact.py:88-101)."""
+
+    if batch <= 0 or kv_heads <= 0 or kv_len <= 0 or kv_len % 64:
+        raise ValueError("batch/kv_heads must be positive and kv_len divisible by 64")
+    pairs = batch * kv_heads
+    needed = -(-target_producer_ctas // pairs)
+    return max(1, min(kv_len // 64, needed))
+
+
+@dataclass
+class ExactDecodePlan:
+    """Allocation-free exact GQA decode over bound buffers."""
+
+    query: torch.Tensor
+    key_cache: torch.Tensor
+    value_cache: torch.Tensor
+    output: torch.Tensor
+    workspace: torch.Tensor
+    num_splits: int
+    kv_layout: str
+    backend: str = SM100_EXACT_BACKEND
+    _plan: native.NativePlan = field(default=None, repr=False)
+
+    @classmethod
+    def build(cls, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, *,
+              output: Optional[torch.Tensor] = None, num_splits: Optional[int] = None,
+              promoted_only: bool = True, kv_layout: Optional[str] = None,
+              seq_lens: Optional[torch.Tensor] = None, kernel: str = "auto") -> "ExactDecodePlan":
+        """Bind a plan.
+
+        ``kv_layout`` is ``"BHND"`` (head-major ``[B, Hkv, N, D]``, what the
+        reference's plan takes) or ``"BNHD"``; by default head-major is assumed,
+        as in the reference.  ``num_splits`` asks for that many CTAs per
+        (row, KV head); ``None`` sizes the grid to the GPU.  ``promoted_only``
+        is accepted for compatibility and has no effect: every supported shape
+        is served.
+        """
+
+        del promoted_only
+        native.require_cuda(query, key_cache, value_cache)
+        layout = kv_layout or "BHND"
+        if query.dim() != 4 or key_cache.dim() != 4 or value_cache.dim() != 4:
+            raise ValueError("unsupported exact decode buffers: rank")
+        batch, _, q_heads, dim = (int(x) for x in query.shape)
+        kv_heads = int(key_cache.shape[1] if layout == "BHND" else key_cache.shape[2])
+        if kv_heads <= 0 or q_heads % kv_heads:
+            raise ValueError("unsupported exact decode buffers: gqa")
+        if output is None:
+            output = torch.empty_like(query)
+        if output.shape != query.shape or output.dtype != query.dtype:
+            raise ValueError("output must match query shape and dtype")
+        if not output.is_cuda or not output.is_contiguous():
+            raise ValueError("output must be a contiguous CUDA tensor")
+        if num_splits is not None and num_splits <= 0:
+            raise ValueError("num_splits must be positive")
+        num_ctas = 0 if num_splits is None else int(num_splits) * batch * kv_heads
+        workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
+        plan = native.exact_plan(query, key_cache, value_cache, output, workspace, kv_layout=layout,
+                                 seq_lens=seq_lens, num_ctas=num_ctas, kernel=kernel)
+        pairs = batch * kv_heads
+        return cls(query=query, key_cache=key_cache, value_cache=value_cache, output=output,
+                   workspace=workspace, num_splits=max(1, -(-plan.num_ctas // pairs)), kv_layout=layout,
+                   _plan=plan)
+
+    @property
+    def workspace_bytes(self) -> int:
+        return self.workspace.numel()
+
+    @property
+    def kernel_name(self) -> str:
+        return self._plan.kernel_name
+
+    @property
+    def num_ctas(self) -> int:
+        return self._plan.num_ctas
+
+    @property
+    def launches_per_run(self) -> int:
+        return self._plan.launches
+
+    def run(self) -> torch.Tensor:
+        self._plan.run()
+        return self.output
+
+    # The reference exposes several launch orders of its two kernels; here they
+    # are one launch, kept as aliases so existing call sites still work.
+    run_two_call = run
+    run_combined = run
+    run_warp_merge = run
+
+    def device_status(self) -> int:
+        """Synchronise and return the kernels' status bits (0 = clean)."""
+
+        return native.workspace_status(self.workspace)
+
+
+def supports_exact_decode(query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor) -> bool:
+    """Whether :class:`ExactDecodePlan` can bind these buffers (CUDA sm_100, matching shapes)."""
+
+    from .decode import _exact_native_supported
+
+    return _exact_native_supported(query, key_cache, value_cache)
+
+
+__all__ = ["ExactDecodePlan", "SM100_EXACT_BACKEND", "choose_num_splits", "infer_kv_layout", "supports_exact_decode"]

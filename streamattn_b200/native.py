@@ -1,0 +1,371 @@
+"""ctypes binding of ``libstreamattn_b200.so`` (the C ABI in ``include/streamattn_b200.h``).
+
+There is no fallback: if the library cannot be loaded (or built with nvcc) every
+entry point raises.  Tensors are passed as raw device pointers plus the current
+CUDA stream handle of their device.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional, Sequence
+
+import torch
+
+from . import build as _build
+
+SA_OK = 0
+SA_ERR_INVALID = 1
+SA_ERR_UNSUPPORTED = 2
+SA_ERR_CUDA = 3
+SA_ERR_DEVICE = 4
+
+SA_DTYPE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+SA_INDEX = {torch.int32: 0, torch.int64: 1}
+SA_LAYOUT = {"NHD": 0, "HND": 1}
+SA_BLOCK_ORDER = {"sequential": 0, "recent_first": 1, "sink_recent_first": 2}
+SA_OUT_FINAL = 0
+SA_OUT_STATE = 1
+SA_KERNEL_AUTO = 0
+SA_KERNEL_STREAM = 1
+SA_KERNEL_GENERIC = 2
+SA_KERNEL = {"auto": SA_KERNEL_AUTO, "stream": SA_KERNEL_STREAM, "generic": SA_KERNEL_GENERIC}
+SA_KERNEL_NAMES = {SA_KERNEL_STREAM: "sm100_tma_mma_stream", SA_KERNEL_GENERIC: "sm100_generic_simt"}
+SA_DEV_PIPELINE_TIMEOUT = 1
+SA_DEV_BAD_PAGE = 2
+SA_MAX_SEED_BLOCKS = 256
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_i64 = ctypes.c_int64
+_sz = ctypes.c_size_t
+_i32p = ctypes.POINTER(ctypes.c_int32)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+
+_EXACT_ARGS = [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _i, _i, _i, _i, _i64,
+               _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i]
+_PAGED_ARGS = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _i, _i, _i, _i, _i, _i64,
+               _i, _i, _i, _i, _i, _i, _i]
+_SEED_COMMON = [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i]
+
+_SIGNATURES = {
+    "sa_version": ([], _i),
+    "sa_last_error": ([], ctypes.c_char_p),
+    "sa_device_supported": ([_i], _i),
+    "sa_device_sm_count": ([_i], _i),
+    "sa_workspace_bytes": ([_i, _i, _i, _i, _i], _sz),
+    "sa_workspace_status": ([_vp, _vp], _i),
+    "sa_exact_decode": (_EXACT_ARGS + [_vp], _i),
+    "sa_paged_decode": (_PAGED_ARGS + [_vp], _i),
+    "sa_seed_blocks": ([_i64, _i, _i, _i, _i, _i, _i32p, _i], _i),
+    "sa_seed_token_indices": ([_i64, _i, _i32p, _i, _i64p, _i64], _i64),
+    "sa_seed_decode": (_SEED_COMMON + [_i, _i, _i, _i, _i, _i, _i, _vp], _i),
+    "sa_seed_decode_blocks": (_SEED_COMMON + [_i, _i32p, _i, _i, _i, _vp], _i),
+    "sa_merge_states": ([_vp, _i, _i64, _i, _vp, _i, _vp], _i),
+    "sa_exact_plan_create": (_EXACT_ARGS, _vp),
+    "sa_paged_plan_create": (_PAGED_ARGS, _vp),
+    "sa_seed_plan_create": (_SEED_COMMON + [_i, _i32p, _i, _i, _i], _vp),
+    "sa_plan_run": ([_vp, _vp], _i),
+    "sa_plan_kernel": ([_vp], _i),
+    "sa_plan_num_ctas": ([_vp], _i),
+    "sa_plan_launches": ([_vp], _i),
+    "sa_plan_destroy": ([_vp], None),
+}
+
+_LOCK = threading.Lock()
+_LIB: Optional[ctypes.CDLL] = None
+
+
+def exported_symbols() -> Sequence[str]:
+    """Names this binding expects the library to export."""
+
+    return tuple(_SIGNATURES)
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first if needed) the native library; raises if impossible."""
+
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = _build.LIB_PATH
+        if _build.is_stale():
+            if path.is_file() and _build.find_nvcc() is None:
+                pass  # a prebuilt library without a compiler: use it as shipped
+            else:
+                path = _build.build()
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise RuntimeError(
+                f"cannot load {path}: {exc}; streamattn_b200 has no CPU or interpreted fallback"
+            ) from exc
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _LIB = lib
+        return lib
+
+
+def last_error() -> str:
+    msg = load().sa_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(rc: int) -> None:
+    """Map a C status code to the exception types of the reference API."""
+
+    if rc == SA_OK:
+        return
+    msg = last_error()
+    if rc in (SA_ERR_INVALID, SA_ERR_UNSUPPORTED):
+        raise ValueError(msg or f"streamattn_b200 native error {rc}")
+    raise RuntimeError(msg or f"streamattn_b200 native error {rc}")
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    """All tensors must live on one CUDA device; there is no CPU execution path."""
+
+    devices = {t.device for t in tensors if t is not None}
+    if len(devices) != 1:
+        raise ValueError("all tensors of a decode call must share one device")
+    device = next(iter(devices))
+    if device.type != "cuda":
+        raise RuntimeError(
+            "streamattn_b200 executes only on CUDA (sm_100) tensors; it has no CPU fallback "
+            f"(got device {device})"
+        )
+    return device
+
+
+def device_supported(device: torch.device) -> bool:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return bool(load().sa_device_supported(int(index)))
+
+
+def stream_handle(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int, num_ctas: int = 0) -> int:
+    n = int(load().sa_workspace_bytes(batch, q_heads, kv_heads, head_dim, num_ctas))
+    if n == 0:
+        raise ValueError(last_error())
+    return n
+
+
+def new_workspace(device: torch.device, batch: int, q_heads: int, kv_heads: int, head_dim: int,
+                  num_ctas: int = 0) -> torch.Tensor:
+    """Zero-filled workspace (the library needs zeros once, then keeps it consistent)."""
+
+    return torch.zeros(workspace_bytes(batch, q_heads, kv_heads, head_dim, num_ctas),
+                       dtype=torch.uint8, device=device)
+
+
+def workspace_status(workspace: torch.Tensor) -> int:
+    with torch.cuda.device(workspace.device):
+        rc = int(load().sa_workspace_status(workspace.data_ptr(), stream_handle(workspace.device)))
+    if rc < 0:
+        raise RuntimeError(last_error())
+    return rc
+
+
+def seed_blocks(kv_len: int, block_size: int, sink_blocks: int, recent_blocks: int,
+                middle_seed_blocks: int, block_order: str) -> list:
+    if block_order not in SA_BLOCK_ORDER:
+        raise ValueError("block_order must be sequential, recent_first, or sink_recent_first")
+    cap = max(1, sink_blocks + recent_blocks + middle_seed_blocks)
+    buf = (ctypes.c_int32 * cap)()
+    n = load().sa_seed_blocks(kv_len, block_size, sink_blocks, recent_blocks, middle_seed_blocks,
+                              SA_BLOCK_ORDER[block_order], buf, cap)
+    if n < 0:
+        raise ValueError(last_error())
+    return [int(buf[i]) for i in range(n)]
+
+
+def seed_token_indices(kv_len: int, block_size: int, blocks: Sequence[int]) -> torch.Tensor:
+    nb = len(blocks)
+    arr = (ctypes.c_int32 * max(1, nb))(*[int(b) for b in blocks])
+    cap = max(1, nb * block_size)
+    out = torch.empty(cap, dtype=torch.int64)
+    n = load().sa_seed_token_indices(kv_len, block_size, arr, nb,
+                                     ctypes.cast(out.data_ptr(), _i64p), cap)
+    if n < 0:
+        raise ValueError(last_error())
+    return out[:n].clone()
+
+
+class NativePlan:
+    """Owner of one ``sa_plan_t``; ``run()`` enqueues on the device's current stream."""
+
+    def __init__(self, handle: int, device: torch.device, keepalive: tuple) -> None:
+        if not handle:
+            msg = last_error()
+            raise ValueError(msg or "native plan creation failed")
+        self._handle = ctypes.c_void_p(handle)
+        self._device = device
+        self._device_index = device.index if device.index is not None else torch.cuda.current_device()
+        self._keepalive = keepalive
+        lib = load()
+        self._run = lib.sa_plan_run
+        self.kernel = int(lib.sa_plan_kernel(self._handle))
+        self.kernel_name = SA_KERNEL_NAMES.get(self.kernel, "unknown")
+        self.num_ctas = int(lib.sa_plan_num_ctas(self._handle))
+        self.launches = int(lib.sa_plan_launches(self._handle))
+
+    def run(self) -> None:
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self._device_index):
+                rc = self._run(self._handle, torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = self._run(self._handle, torch.cuda.current_stream().cuda_stream)
+        if rc:
+            check(rc)
+
+    def __del__(self) -> None:
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle and _LIB is not None:
+            _LIB.sa_plan_destroy(handle)
+
+
+def _q_strides(query: torch.Tensor) -> tuple:
+    """query is [B,1,Hq,D] with D contiguous; returns (stride_b, stride_h) in elements."""
+
+    if query.dim() != 4 or query.shape[1] != 1:
+        raise ValueError("decode query must be [batch, 1, heads, dim]")
+    if query.stride(3) != 1 and query.shape[3] > 1:
+        raise ValueError("query head_dim must be contiguous")
+    return int(query.stride(0)), int(query.stride(2))
+
+
+def _kv_geometry(key: torch.Tensor, value: torch.Tensor, kv_layout: str) -> tuple:
+    """Returns (kv_heads, kv_len, stride_b, stride_n, stride_h) for BNHD / BHND caches."""
+
+    if key.shape != value.shape or key.stride() != value.stride():
+        raise ValueError("key_cache and value_cache must have identical shape and strides")
+    if key.stride(3) != 1 and key.shape[3] > 1:
+        raise ValueError("cache head_dim must be contiguous")
+    if kv_layout == "BNHD":
+        return int(key.shape[2]), int(key.shape[1]), int(key.stride(0)), int(key.stride(1)), int(key.stride(2))
+    if kv_layout == "BHND":
+        return int(key.shape[1]), int(key.shape[2]), int(key.stride(0)), int(key.stride(2)), int(key.stride(1))
+    raise ValueError("kv_layout must be BNHD or BHND")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else int(t.data_ptr())
+
+
+def exact_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
+               workspace: torch.Tensor, *, kv_layout: str = "BNHD",
+               seq_lens: Optional[torch.Tensor] = None, out_state: bool = False,
+               num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
+    device = require_cuda(query, key, value, output, workspace, seq_lens)
+    if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, value, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    if int(key.shape[0]) != batch or int(key.shape[3]) != dim:
+        raise ValueError("query/KV batch and head_dim must match")
+    _check_output(output, query, out_state)
+    lens_dtype = SA_INDEX[seq_lens.dtype] if seq_lens is not None else 0
+    with torch.cuda.device(device):
+        handle = load().sa_exact_plan_create(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(workspace), workspace.numel(),
+            _ptr(seq_lens), lens_dtype, batch, q_heads, kv_heads, dim, kv_len,
+            q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), SA_KERNEL[kernel],
+        )
+    return NativePlan(handle, device, (query, key, value, output, workspace, seq_lens))
+
+
+def _check_output(output: torch.Tensor, query: torch.Tensor, out_state: bool) -> None:
+    batch, _, q_heads, dim = map(int, query.shape)
+    if not output.is_contiguous():
+        raise ValueError("output must be contiguous")
+    if out_state:
+        if output.dtype != torch.float32 or tuple(output.shape) != (batch, q_heads, dim + 2):
+            raise ValueError("state output must be float32 [batch, heads, dim + 2]")
+    elif output.shape != query.shape or output.dtype != query.dtype:
+        raise ValueError("output must match query shape and dtype")
+
+
+def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.Tensor,
+               page_table: torch.Tensor, seq_lens: torch.Tensor, output: torch.Tensor,
+               workspace: torch.Tensor, *, layout: str, trace: Optional[torch.Tensor] = None,
+               out_state: bool = False, num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
+    device = require_cuda(query, key_pages, value_pages, page_table, seq_lens, output, workspace, trace)
+    layout = layout.upper()
+    if layout not in SA_LAYOUT:
+        raise ValueError("paged KV layout must be NHD or HND")
+    if query.dtype not in SA_DTYPE or key_pages.dtype != query.dtype or value_pages.dtype != query.dtype:
+        raise ValueError("query and paged key/value dtypes must match (bf16, fp16 or fp32)")
+    tensors = (query, key_pages, value_pages, page_table, seq_lens)
+    if not all(t.is_contiguous() for t in tensors):
+        raise ValueError("query and paged cache tensors must be contiguous")
+    batch, _, q_heads, dim = map(int, query.shape)
+    num_pages = int(key_pages.shape[0])
+    if layout == "NHD":
+        page_size, kv_heads = int(key_pages.shape[1]), int(key_pages.shape[2])
+    else:
+        kv_heads, page_size = int(key_pages.shape[1]), int(key_pages.shape[2])
+    if trace is not None and (trace.dtype != torch.int32 or trace.shape != page_table.shape
+                              or not trace.is_contiguous()):
+        raise ValueError("trace must be a contiguous int32 tensor shaped like page_table")
+    _check_output(output, query, out_state)
+    with torch.cuda.device(device):
+        handle = load().sa_paged_plan_create(
+            _ptr(query), _ptr(key_pages), _ptr(value_pages), _ptr(page_table), _ptr(seq_lens),
+            _ptr(output), _ptr(workspace), workspace.numel(), _ptr(trace),
+            batch, q_heads, kv_heads, dim, page_size, int(page_table.shape[1]), num_pages,
+            SA_LAYOUT[layout], SA_DTYPE[query.dtype], SA_INDEX[page_table.dtype], SA_INDEX[seq_lens.dtype],
+            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), SA_KERNEL[kernel],
+        )
+    return NativePlan(handle, device,
+                      (query, key_pages, value_pages, page_table, seq_lens, output, workspace, trace))
+
+
+def seed_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
+              workspace: torch.Tensor, *, block_size: int, blocks: Sequence[int],
+              kv_layout: str = "BNHD", num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
+    device = require_cuda(query, key, value, output, workspace)
+    if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, value, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    if int(key.shape[0]) != batch or int(key.shape[3]) != dim:
+        raise ValueError("query/KV batch and head_dim must match")
+    _check_output(output, query, False)
+    nb = len(blocks)
+    arr = (ctypes.c_int32 * max(1, nb))(*[int(b) for b in blocks])
+    with torch.cuda.device(device):
+        handle = load().sa_seed_plan_create(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(workspace), workspace.numel(),
+            batch, q_heads, kv_heads, dim, kv_len, q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+            int(block_size), arr, nb, int(num_ctas), SA_KERNEL[kernel],
+        )
+    return NativePlan(handle, device, (query, key, value, output, workspace))
+
+
+def merge_states(states: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
+    """states [parts, rows, D+2] float32 -> output [rows, D] (any supported dtype)."""
+
+    device = require_cuda(states, output)
+    if states.dtype != torch.float32 or states.dim() != 3 or not states.is_contiguous():
+        raise ValueError("states must be a contiguous float32 [parts, rows, dim + 2] tensor")
+    parts, rows, width = map(int, states.shape)
+    dim = width - 2
+    if output.dtype not in SA_DTYPE or output.numel() != rows * dim or not output.is_contiguous():
+        raise ValueError("output must be contiguous with rows * dim elements")
+    with torch.cuda.device(device):
+        rc = load().sa_merge_states(states.data_ptr(), parts, rows, dim, output.data_ptr(),
+                                    SA_DTYPE[output.dtype], stream_handle(device))
+    check(rc)
+    return output
