@@ -1,0 +1,450 @@
+"""Benchmark of the decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one decode call over one batch of synthetic K/V already resident in
+HBM.  The metric is achieved KV-bytes/s (algorithmic bytes of the call divided by
+its time); ``ms_per_step`` is the time of one call.
+
+Workloads (BASELINE.json configs):
+  exact_c2   exact contiguous GQA decode, B8 Hq16 Hkv2 D64 N65536 bf16, head-major KV   [default at N=1]
+  exact_c2_bnhd  same values in the public BNHD layout
+  paged_c3   paged HND page-16, ragged lengths U[16384, 65536], random page order
+  seed_c4    seed-only decode, Qwen2.5-3B attention shape, 384 seed tokens of 32768
+  cp_c5      context-parallel exact decode, B1 Hq32 Hkv8 D128 N1048576 sharded over N GPUs
+             (strong scaling; state all-gather over NCCL + merge)                       [default at N>1]
+
+Under torchrun (N>1) every rank runs; timing is the max over ranks of CUDA-event
+time between a barrier + synchronize on both sides.  ``--impl reference`` times the
+reference's CPU PyTorch path (restated in ``oracle/torch_port.py``) on the host
+cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "kv_bytes_per_second"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (None until a capture exists for the workload).
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period_s: float = 0.004) -> None:
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _sample_once(self) -> None:
+        nv = self._nvml
+        try:
+            self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = int(get(self._handle))
+            for bit, name in self.REASONS.items():
+                if bits & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            self._sample_once()
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._sample_once()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+            self._sample_once()
+
+    def summary(self) -> dict:
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def _randn_bf16(shape, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).bfloat16()
+
+
+# --------------------------------------------------------------------------
+# Workloads: each returns (run_fn, q_device, out_device, info)
+# --------------------------------------------------------------------------
+
+def build_exact_c2(device, layout="BHND"):
+    import streamattn_b200 as sa
+
+    B, Hq, Hkv, D, N = 8, 16, 2, 64, 65536
+    q = _randn_bf16((B, 1, Hq, D), 0, device)
+    k = _randn_bf16((B, Hkv, N, D), 1, device)
+    v = _randn_bf16((B, Hkv, N, D), 2, device)
+    if layout == "BNHD":
+        k, v = k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous()
+    plan = sa.ExactDecodePlan.build(q, k, v, kv_layout=layout)
+    info = dict(workload="exact_c2" if layout == "BHND" else "exact_c2_bnhd", batch=B, q_heads=Hq, kv_heads=Hkv,
+                head_dim=D, kv_len=N, kv_layout=layout, kernel=plan.kernel_name, ctas=plan.num_ctas,
+                bytes=2 * B * Hkv * N * D * 2, launches=plan.launches_per_run)
+    return plan.run, q, plan.output, info, plan
+
+
+def build_paged_c3(device):
+    import streamattn_b200 as sa
+
+    B, Hq, Hkv, D, page, cap = 8, 16, 2, 64, 16, 65536
+    max_pages = cap // page
+    pool = B * max_pages
+    g = torch.Generator().manual_seed(17)
+    q = _randn_bf16((B, 1, Hq, D), 3, device)
+    k = _randn_bf16((pool, Hkv, page, D), 4, device)
+    v = _randn_bf16((pool, Hkv, page, D), 5, device)
+    table = torch.randperm(pool, generator=g).to(torch.int32).view(B, max_pages)
+    lengths = torch.randint(16384, 65537, (B,), generator=g).to(torch.int32)
+    for b in range(B):
+        table[b, -(-int(lengths[b]) // page):] = -1
+    cache = sa.PagedKVCache(key=k, value=v, page_table=table.to(device), sequence_lengths=lengths.to(device),
+                            layout="HND")
+    plan = sa.PagedExactDecodePlan.build(q, cache)
+    tokens = int(lengths.sum())
+    pages = int(sum(-(-int(n) // page) for n in lengths))
+    info = dict(workload="paged_c3", batch=B, q_heads=Hq, kv_heads=Hkv, head_dim=D, page_size=page, capacity=cap,
+                total_tokens=tokens, kernel=plan.kernel_name, ctas=plan.num_ctas,
+                bytes=2 * Hkv * D * 2 * tokens + 4 * pages, launches=plan.launches_per_run)
+    return plan.run, q, plan.output, info, plan
+
+
+def build_seed_c4(device):
+    import streamattn_b200 as sa
+    from streamattn_b200 import native
+
+    B, Hq, Hkv, D, N, bs = 8, 16, 2, 128, 32768, 16
+    g = torch.Generator().manual_seed(0)
+    q = _randn_bf16((B, 1, Hq, D), 6, device)
+    k = _randn_bf16((B, N, Hkv, D), 7, device)
+    v = _randn_bf16((B, N, Hkv, D), 8, device)
+    middle = (torch.randperm(2032 - 4, generator=g)[:4] + 4).tolist()
+    blocks = [0, 1, 2, 3, *middle, *range(2032, 2048)]
+    out = torch.empty_like(q)
+    ws = native.new_workspace(device, B, Hq, Hkv, D)
+    plan = native.seed_plan(q, k, v, out, ws, block_size=bs, blocks=blocks)
+    info = dict(workload="seed_c4", batch=B, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, seed_tokens=384,
+                kernel=plan.kernel_name, ctas=plan.num_ctas, bytes=2 * B * Hkv * 384 * D * 2,
+                launches=plan.launches, l2="seed set (3 MB) stays L2-resident between calls")
+    return plan.run, q, out, info, plan
+
+
+def build_cp_c5(device, rank, world):
+    from streamattn_b200.context_parallel import ContextParallelExactDecode, shard_bounds
+
+    Hq, Hkv, D, N = 32, 8, 128, 1048576
+    chunk = 65536
+    lo, hi = shard_bounds(N, world, rank)
+    q = _randn_bf16((1, 1, Hq, D), 100, device)
+    k = torch.empty(1, Hkv, hi - lo, D, dtype=torch.bfloat16, device=device)
+    v = torch.empty_like(k)
+    # Values depend only on the global chunk index, not on how many GPUs share the sequence.
+    for c0 in range(lo - lo % chunk, hi, chunk):
+        kc = _randn_bf16((1, Hkv, chunk, D), 1000 + 2 * (c0 // chunk), device)
+        vc = _randn_bf16((1, Hkv, chunk, D), 1001 + 2 * (c0 // chunk), device)
+        a, b = max(lo, c0), min(hi, c0 + chunk)
+        k[:, :, a - lo:b - lo] = kc[:, :, a - c0:b - c0]
+        v[:, :, a - lo:b - lo] = vc[:, :, a - c0:b - c0]
+        del kc, vc
+    cp = ContextParallelExactDecode(q, k, v, kv_layout="BHND")
+    info = dict(workload="cp_c5", batch=1, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, shard_tokens=hi - lo,
+                kernel=cp.kernel_name, ctas=cp._plan.num_ctas, bytes=2 * Hkv * N * D * 2,
+                exchange_bytes_per_rank=cp.exchange_bytes_per_rank,
+                launches=2 if world == 1 else 3, parallelism=f"cp{world}")
+    return cp.run, q, cp.output, info, cp
+
+
+def time_region(fn, steps, device):
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize(device)
+    return start.elapsed_time(stop) * 1e-3
+
+
+def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1) -> dict:
+    """Reference CPU path (oracle port) on a bounded sample of the workload."""
+
+    from oracle import torch_port
+
+    cores = torch.get_num_threads()
+    g = torch.Generator().manual_seed(0)
+    if workload in ("exact_c2", "exact_c2_bnhd", "cp_c5"):
+        if workload == "cp_c5":
+            B, Hq, Hkv, D, N, note = 1, 32, 8, 128, 65536, "65536 of 1048576 tokens of the row, fp32 on CPU"
+        else:
+            B, Hq, Hkv, D, N, note = 2, 16, 2, 64, 65536, "2 of 8 rows at full kv_len 65536, fp32 on CPU"
+        q = torch.randn(B, 1, Hq, D, generator=g)
+        k = torch.randn(B, N, Hkv, D, generator=g)
+        v = torch.randn(B, N, Hkv, D, generator=g)
+        fn = lambda: torch_port.dense_decode(q, k, v)
+        alg = 2 * B * Hkv * N * D * 2
+    elif workload == "paged_c3":
+        B, Hq, Hkv, D, page, n = 1, 16, 2, 64, 16, 4096
+        q = torch.randn(B, 1, Hq, D, generator=g)
+        k = torch.randn(n // page, Hkv, page, D, generator=g)
+        v = torch.randn(n // page, Hkv, page, D, generator=g)
+        table = torch.randperm(n // page, generator=g).to(torch.int32).view(1, -1)
+        lens = torch.tensor([n], dtype=torch.int32)
+        fn = lambda: torch_port.paged_decode(q, k, v, table, lens, layout="HND")
+        alg = 2 * Hkv * D * 2 * n
+        note = "1 row of 4096 tokens (page-streaming python loop of the reference), fp32 on CPU"
+        steps, warmup = 1, 0
+    else:
+        B, Hq, Hkv, D, N = 8, 16, 2, 128, 32768
+        q = torch.randn(B, 1, Hq, D, generator=g)
+        k = torch.randn(B, N, Hkv, D, generator=g)
+        v = torch.randn(B, N, Hkv, D, generator=g)
+        tokens = torch.cat([torch.arange(64), torch.arange(32448, 32768)])
+        fn = lambda: torch_port.seed_decode(q, k, v, tokens)
+        alg = 2 * B * Hkv * 384 * D * 2
+        note = "full config-4 shape, 384 seed tokens, fp32 on CPU"
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": alg / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port", "sample": note,
+            "ms_per_sample": dt * 1e3}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto",
+                    choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "cp_c5"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload
+    if workload == "auto":
+        workload = "exact_c2" if max(world, args.gpus) == 1 else "cp_c5"
+    warmup = max(3, args.warmup)
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base = cpu_baseline_sample(workload, steps=max(1, min(args.steps, 5)), warmup=min(warmup, 1))
+        line = {
+            "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample"],
+            "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": workload, "sample": base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    elif workload == "cp_c5":
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29555")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        distributed = True
+
+    if workload == "exact_c2":
+        run, q_dev, out_dev, info, plan = build_exact_c2(device)
+    elif workload == "exact_c2_bnhd":
+        run, q_dev, out_dev, info, plan = build_exact_c2(device, "BNHD")
+    elif workload == "paged_c3":
+        run, q_dev, out_dev, info, plan = build_paged_c3(device)
+    elif workload == "seed_c4":
+        run, q_dev, out_dev, info, plan = build_seed_c4(device)
+    else:
+        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world)
+    alg_bytes = info.pop("bytes")
+    launches = info.pop("launches")
+
+    def barrier():
+        if distributed:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(x: float) -> float:
+        if not distributed or world == 1:
+            return x
+        import torch.distributed as dist
+
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- kernel-resident timing: inputs already in HBM ----
+    for _ in range(warmup):
+        run()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        elapsed = time_region(run, args.steps, device)
+        if len(clocks.samples) < 4:  # very short region: keep the same kernel busy until NVML has samples
+            t_end = time.perf_counter() + 0.3
+            while time.perf_counter() < t_end:
+                for _ in range(50):
+                    run()
+                torch.cuda.synchronize(device)
+    barrier()
+    elapsed = max_over_ranks(elapsed)
+    step_s = elapsed / args.steps
+
+    # ---- end to end through the public plan API with host buffers ----
+    q_host = q_dev.cpu().pin_memory()
+    out_host = torch.empty(out_dev.shape, dtype=out_dev.dtype).pin_memory()
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        run()
+        out_host.copy_(out_dev, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    for _ in range(warmup):
+        e2e_step()
+    barrier()
+    e2e_steps = max(10, args.steps // 4)
+    e2e_elapsed = max_over_ranks(time_region(e2e_step, e2e_steps, device))
+    barrier()
+    e2e_s = e2e_elapsed / e2e_steps
+
+    status = plan.device_status() if hasattr(plan, "device_status") else 0
+    peak, peak_kind = measured_hbm_peak()
+    per_gpu_bytes = alg_bytes / world if workload == "cp_c5" else alg_bytes
+    achieved = per_gpu_bytes / step_s / 1e9
+
+    single_gpu_us = None
+    if workload == "cp_c5" and world > 1 and rank == 0:
+        # One-GPU time of the same 1M-token row, measured in this run on rank 0 (not in the timed region).
+        full = build_cp_c5_single(device)
+        for _ in range(3):
+            full()
+        single_gpu_us = time_region(full, 10, device) / 10 * 1e6
+    if distributed:
+        barrier()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": alg_bytes / step_s / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": step_s * 1e3, "us_per_call": step_s * 1e6,
+            "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {**info, "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2"),
+                       "timing": "CUDA events around K back-to-back calls, max over ranks"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(workload),
+                         "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8tbs": achieved / 8000.0,
+                         "kernel": info["kernel"], "algorithmic_bytes_per_launch": per_gpu_bytes},
+            "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "us_per_call": e2e_s * 1e6,
+                    "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
+                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
+                    "note": "query from pinned host memory in, output to pinned host memory out, every step; "
+                            "the KV cache is resident device state bound to the plan"},
+            "gpu_launches": args.steps * launches,
+            "clocks": clocks.summary(),
+            "device_status": status,
+        }
+        if single_gpu_us is not None:
+            line["cp_single_gpu_us"] = single_gpu_us
+            line["cp_speedup_vs_1gpu"] = single_gpu_us / (step_s * 1e6)
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline_sample(workload)
+        print(json.dumps(line))
+    if distributed:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def build_cp_c5_single(device):
+    """The whole 1M-token config-5 row on one GPU (local kernel + merge, no collective)."""
+
+    import streamattn_b200 as sa
+
+    Hq, Hkv, D, N = 32, 8, 128, 1048576
+    q = _randn_bf16((1, 1, Hq, D), 100, device)
+    k = torch.empty(1, Hkv, N, D, dtype=torch.bfloat16, device=device)
+    v = torch.empty_like(k)
+    chunk = 65536
+    for c0 in range(0, N, chunk):
+        k[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1000 + 2 * (c0 // chunk), device)
+        v[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1001 + 2 * (c0 // chunk), device)
+    plan = sa.ExactDecodePlan.build(q, k, v, kv_layout="BHND")
+    return plan.run
+
+
+if __name__ == "__main__":
+    main()

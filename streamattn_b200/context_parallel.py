@@ -1,0 +1,118 @@
+"""Multi-GPU decode: context-parallel exact decode and request sharding.
+
+The reference has no multi-GPU decode path.  Softmax attention over a token
+partition is exactly mergeable from per-shard ``(m, l, o)`` states, so a long
+KV sequence can be split across the GPUs of one box:
+
+* rank r owns tokens ``[r*N/G, (r+1)*N/G)`` of every (row, KV head);
+* each rank runs the exact kernel on its shard and emits the split state
+  ``[B, Hq, D+2]`` (float32) instead of a normalised output;
+* one all-gather (NCCL over NVLink) brings the G states into each rank's own
+  memory and a local merge kernel produces the final output on every rank.
+
+The exchange is ``B*Hq*(D+2)*4`` bytes per rank (16.6 KB for one row of 32
+heads of 128), so it is latency- not bandwidth-bound.  Batch-parallel shapes
+shard by request and need no collective (:func:`shard_requests`).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import native
+
+
+def shard_bounds(kv_len: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Token range ``[lo, hi)`` of ``rank`` when ``kv_len`` tokens are split evenly."""
+
+    if kv_len < 0 or world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("bad shard arguments")
+    return kv_len * rank // world_size, kv_len * (rank + 1) // world_size
+
+
+def shard_requests(batch: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Row range ``[lo, hi)`` of ``rank`` for batch-parallel decode (no collective)."""
+
+    return shard_bounds(batch, world_size, rank)
+
+
+def gather_states(local_state: torch.Tensor, gathered: Optional[torch.Tensor] = None,
+                  group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather the per-rank split states into ``[world, B, Hq, D+2]`` on every rank."""
+
+    world = dist.get_world_size(group)
+    if gathered is None:
+        gathered = local_state.new_empty((world, *local_state.shape))
+    if tuple(gathered.shape) != (world, *local_state.shape) or not gathered.is_contiguous():
+        raise ValueError("gathered must be a contiguous [world, *local_state.shape] tensor")
+    # Concatenation form (world*B leading rows): accepted by both the NCCL and the gloo backend.
+    flat = gathered.view(world * local_state.shape[0], *local_state.shape[1:])
+    dist.all_gather_into_tensor(flat, local_state.contiguous(), group=group)
+    return gathered
+
+
+class ContextParallelExactDecode:
+    """Exact decode over a KV sequence sharded across the ranks of a process group.
+
+    Bound once to this rank's shard; ``run()`` launches the local kernel, the
+    all-gather and the merge on the current stream and allocates nothing.
+    ``key_shard`` / ``value_shard`` hold this rank's tokens only, in ``kv_layout``
+    (``"BHND"`` head-major by default).  ``shard_lens`` optionally gives per-row
+    valid token counts inside the shard (ragged rows).
+    """
+
+    def __init__(self, query: torch.Tensor, key_shard: torch.Tensor, value_shard: torch.Tensor, *,
+                 kv_layout: str = "BHND", group: Optional[dist.ProcessGroup] = None,
+                 output: Optional[torch.Tensor] = None, shard_lens: Optional[torch.Tensor] = None,
+                 num_ctas: int = 0, kernel: str = "auto") -> None:
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed must be initialised for context-parallel decode")
+        native.require_cuda(query, key_shard, value_shard)
+        self.group = group
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.query = query
+        batch, _, q_heads, dim = (int(x) for x in query.shape)
+        kv_heads = int(key_shard.shape[1] if kv_layout == "BHND" else key_shard.shape[2])
+        self.output = torch.empty_like(query) if output is None else output
+        self.local_state = torch.empty(batch, q_heads, dim + 2, dtype=torch.float32, device=query.device)
+        self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
+                                    device=query.device)
+        self.workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
+        self._plan = native.exact_plan(query, key_shard, value_shard, self.local_state, self.workspace,
+                                       kv_layout=kv_layout, seq_lens=shard_lens, out_state=True,
+                                       num_ctas=num_ctas, kernel=kernel)
+        self._rows = batch * q_heads
+        self._dim = dim
+
+    @property
+    def kernel_name(self) -> str:
+        return self._plan.kernel_name
+
+    @property
+    def exchange_bytes_per_rank(self) -> int:
+        return self.local_state.numel() * 4
+
+    def device_status(self) -> int:
+        """Synchronise and return the local kernel's status bits (0 = clean)."""
+
+        return native.workspace_status(self.workspace)
+
+    def run_local(self) -> torch.Tensor:
+        """Only the local shard kernel; returns this rank's state."""
+
+        self._plan.run()
+        return self.local_state
+
+    def run(self) -> torch.Tensor:
+        self._plan.run()
+        if self.world_size == 1:
+            states = self.local_state.view(1, self._rows, self._dim + 2)
+        else:
+            gather_states(self.local_state, self.gathered, self.group)
+            states = self.gathered.view(self.world_size, self._rows, self._dim + 2)
+        native.merge_states(states, self.output)
+        return self.output
