@@ -276,6 +276,8 @@ def main() -> None:
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "cp_c5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="only warm-up + the timed region (for runs under ncu): no e2e, CPU or clock legs")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -353,7 +355,7 @@ def main() -> None:
     barrier()
     with ClockSampler(local_rank) as clocks:
         elapsed = time_region(run, args.steps, device)
-        if len(clocks.samples) < 4:  # very short region: keep the same kernel busy until NVML has samples
+        if len(clocks.samples) < 4 and not args.profile:  # very short region: keep the same kernel busy until NVML has samples
             t_end = time.perf_counter() + 0.3
             while time.perf_counter() < t_end:
                 for _ in range(50):
@@ -362,6 +364,15 @@ def main() -> None:
     barrier()
     elapsed = max_over_ranks(elapsed)
     step_s = elapsed / args.steps
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": workload, "us_per_call": step_s * 1e6}))
+        if distributed:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the public plan API with host buffers ----
     q_host = q_dev.cpu().pin_memory()
