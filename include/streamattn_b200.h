@@ -105,6 +105,43 @@ SA_API int sa_exact_decode(const void *q, const void *k, const void *v, void *ou
                            sa_stream_t stream);
 
 /*
+ * sa_exact_decode_static - sa_exact_decode for callers that must not allocate.
+ * It has no counterpart in the reference.
+ *
+ * Some callers cannot obtain a workspace: code running under an allocator that
+ * was handed all of the GPU's memory at start-up (a serving engine that gives
+ * every free byte to its KV-cache pool, so a later cudaMalloc fails), code on a
+ * path where an allocation would synchronise the device (inside a latency-bound
+ * decode loop), or a plugin that is only ever given the tensors of the call.
+ * For them the split states, arrival counters and status word live in a fixed
+ * array inside the library's device image (SA_STATIC_SCRATCH_BYTES, 2 MiB, held
+ * by every GPU that loads the library for the life of the process).  The call
+ * takes the same arguments as sa_exact_decode minus the workspace and computes
+ * the same result with the same kernels.  It calls no cudaMalloc, cudaFree or
+ * other allocating routine.
+ *
+ * Limits and rules:
+ *  - shapes whose split states do not fit the array are refused with
+ *    SA_ERR_UNSUPPORTED (nothing is launched); use sa_exact_decode then.
+ *    With num_ctas = 0 the need is about
+ *    512 + 4*batch*q_heads + 4*(148 + batch*kv_heads)*(q_heads/kv_heads)*(head_dim+2) bytes;
+ *  - the first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    outside any stream capture;
+ *  - all calls on a device share the one array: calls that may overlap on the
+ *    GPU (different streams) race and give wrong results.  Calls on one stream
+ *    are safe; each call clears the counters it needs before launching.
+ */
+#define SA_STATIC_SCRATCH_BYTES (2 * 1024 * 1024)
+SA_API int sa_exact_decode_static(const void *q, const void *k, const void *v, void *out,
+                                  const void *seq_lens, int lens_dtype,
+                                  int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                  int64_t q_stride_b, int64_t q_stride_h,
+                                  int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                  int dtype, int out_mode, int num_ctas, int kernel_choice,
+                                  sa_stream_t stream);
+
+/*
  * Paged exact decode over a page pool with a page table and ragged per-row
  * lengths.  Replaces paged_exact_decode_out, paged_fragmented_exact_decode_out,
  * paged_fragmented_ragged_exact_decode_out

@@ -559,6 +559,68 @@ int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_d
     return SA_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Exact decode without any allocation: the scratch lives in this module's image.
+// ---------------------------------------------------------------------------
+
+// Split states + arrival counters + status word of sa_exact_decode_static.  A
+// file-scope device array: every GPU that loads the library holds these bytes
+// until the process exits.  In host code this name is only a stand-in for the
+// symbol, never a device address; the address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[SA_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_static_scratch on the current device, looked up once per
+// device (with that device current) and remembered.
+int static_scratch_address(void **out)
+{
+    static std::mutex mu;
+    static void *address[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return fail_cuda(err, "sa_exact_decode_static: cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(SA_ERR_DEVICE, "sa_exact_decode_static: device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
+    if (address[dev] == nullptr) {
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (err != cudaSuccess || ptr == nullptr)
+            return fail_cuda(err, "sa_exact_decode_static: cudaGetSymbolAddress");
+        address[dev] = ptr;
+    }
+    *out = address[dev];
+    return SA_OK;
+}
+
+}  // namespace
+
+int sa_exact_decode_static(const void *q, const void *k, const void *v, void *out, const void *seq_lens,
+                           int lens_dtype, int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                           int64_t q_stride_b, int64_t q_stride_h, int64_t kv_stride_b, int64_t kv_stride_n,
+                           int64_t kv_stride_h, int dtype, int out_mode, int num_ctas, int kernel_choice,
+                           sa_stream_t stream)
+{
+    void *scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    sa_plan plan;
+    rc = fill_exact(&plan, q, k, v, out, scratch, SA_STATIC_SCRATCH_BYTES, seq_lens, lens_dtype, batch, q_heads,
+                    kv_heads, head_dim, kv_len, q_stride_b, q_stride_h, kv_stride_b, kv_stride_n, kv_stride_h, dtype,
+                    out_mode, num_ctas, kernel_choice);
+    if (rc == SA_ERR_INVALID && std::strstr(g_error, "workspace too small") != nullptr)
+        return fail(SA_ERR_UNSUPPORTED,
+                    "sa_exact_decode_static: this shape needs more than the %d bytes of built-in scratch; "
+                    "use sa_exact_decode with a caller-provided workspace", SA_STATIC_SCRATCH_BYTES);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left.  The arrival counters and the
+    // status word must start at zero, so clear that prefix on the caller's stream.
+    const size_t prefix = kStatusWords * 4 + counters_bytes(batch, q_heads);
+    cudaError_t err = cudaMemsetAsync(scratch, 0, prefix, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_exact_decode_static: clearing the scratch prefix");
+    return run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
 sa_plan_t *sa_exact_plan_create(const void *q, const void *k, const void *v, void *out, void *workspace,
                                 size_t workspace_bytes, const void *seq_lens, int lens_dtype, int batch, int q_heads,
                                 int kv_heads, int head_dim, int64_t kv_len, int64_t q_stride_b, int64_t q_stride_h,

@@ -57,6 +57,8 @@ _SIGNATURES = {
     "sa_workspace_bytes": ([_i, _i, _i, _i, _i], _sz),
     "sa_workspace_status": ([_vp, _vp], _i),
     "sa_exact_decode": (_EXACT_ARGS + [_vp], _i),
+    "sa_exact_decode_static": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i64,
+                                _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _vp], _i),
     "sa_paged_decode": (_PAGED_ARGS + [_vp], _i),
     "sa_seed_blocks": ([_i64, _i, _i, _i, _i, _i, _i32p, _i], _i),
     "sa_seed_token_indices": ([_i64, _i, _i32p, _i, _i64p, _i64], _i64),
@@ -294,6 +296,39 @@ def _check_output(output: torch.Tensor, query: torch.Tensor, out_state: bool) ->
             raise ValueError("state output must be float32 [batch, heads, dim + 2]")
     elif output.shape != query.shape or output.dtype != query.dtype:
         raise ValueError("output must match query shape and dtype")
+
+
+def exact_decode_static(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor, *,
+                        kv_layout: str = "BNHD", seq_lens: Optional[torch.Tensor] = None,
+                        out_state: bool = False, num_ctas: int = 0, kernel: str = "auto") -> torch.Tensor:
+    """Exact decode with the library's built-in scratch (``sa_exact_decode_static``).
+
+    For callers that cannot allocate a workspace (all device memory already
+    owned by another allocator, or allocation not allowed on the calling path).
+    Nothing is allocated here or in the library.  Shapes whose split states
+    exceed the 2 MiB built-in array raise ``ValueError``.  Calls on one device
+    share that array: issue them on one stream, never concurrently.  The first
+    call on a device should happen outside any CUDA stream capture.
+    """
+
+    device = require_cuda(query, key, value, output, seq_lens)
+    if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, value, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    if int(key.shape[0]) != batch or int(key.shape[3]) != dim:
+        raise ValueError("query/KV batch and head_dim must match")
+    _check_output(output, query, out_state)
+    lens_dtype = SA_INDEX[seq_lens.dtype] if seq_lens is not None else 0
+    with torch.cuda.device(device):
+        rc = load().sa_exact_decode_static(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(seq_lens), lens_dtype,
+            batch, q_heads, kv_heads, dim, kv_len, q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), SA_KERNEL[kernel], stream_handle(device),
+        )
+    check(rc)
+    return output
 
 
 def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.Tensor,
