@@ -35,6 +35,9 @@ import torch
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# Keep stdout to the one JSON line: NCCL prints a version banner there at INFO/VERSION level.
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 METRIC = "kv_bytes_per_second"
 UNIT = "GB/s"

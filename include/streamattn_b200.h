@@ -124,7 +124,7 @@ SA_API int sa_exact_decode(const void *q, const void *k, const void *v, void *ou
  *  - shapes whose split states do not fit the array are refused with
  *    SA_ERR_UNSUPPORTED (nothing is launched); use sa_exact_decode then.
  *    With num_ctas = 0 the need is about
- *    512 + 4*batch*q_heads + 4*(148 + batch*kv_heads)*(q_heads/kv_heads)*(head_dim+2) bytes;
+ *    512 + 4*batch*q_heads + 4*(148 + batch*kv_heads)*(q_heads/kv_heads)*(head_dim+4) bytes;
  *  - the first call on each device looks the array's device address up
  *    (cudaGetSymbolAddress, with that device current); make that first call
  *    outside any stream capture;

@@ -45,7 +45,7 @@ size_t counters_bytes(int batch, int q_heads) { return round_up(static_cast<size
 size_t stream_partial_floats(int batch, int q_heads, int kv_heads, int head_dim, int ctas)
 {
     const size_t group = static_cast<size_t>(q_heads / kv_heads);
-    return (static_cast<size_t>(ctas) + static_cast<size_t>(batch) * kv_heads) * group * (head_dim + 2);
+    return (static_cast<size_t>(ctas) + static_cast<size_t>(batch) * kv_heads) * group * (head_dim + 4);
 }
 
 size_t workspace_bytes_impl(int batch, int q_heads, int kv_heads, int head_dim, int num_ctas)
@@ -125,6 +125,7 @@ bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
 
 struct sa_plan {
     sa::Problem problem;
+    int device;  // device that was current when the plan was made
     bool use_stream;
     sa::StreamGeometry geo;
     int generic_splits;
@@ -143,7 +144,12 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
     const int group = p.q_heads / p.kv_heads;
     if (group > 16) { *why = "more than 16 query heads per KV head"; return false; }
     if (p.batch > 8192) { *why = "batch larger than 8192"; return false; }
+    if (stream_smem_bytes(p.head_dim, group > 8, stream_stages(p.head_dim, group > 8), p.batch) > kStreamSmemLimit) {
+        *why = "batch too large for the shared-memory schedule table";
+        return false;
+    }
     if (reinterpret_cast<uintptr_t>(p.q) % 4 || p.q_sb % 2 || p.q_sh % 2) { *why = "query not 4-byte aligned"; return false; }
+    if (reinterpret_cast<uintptr_t>(p.out) % 16) { *why = "output not 16-byte aligned"; return false; }
     if (max_vlen <= 0 || max_vlen >= (1ll << 31)) { *why = "sequence length out of range"; return false; }
     const int tile = stream_tile_tokens(p.head_dim);
     const SeqDesc &s = p.seq;
@@ -196,6 +202,7 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
         return false;
     }
     const int64_t tiles = static_cast<int64_t>(p.batch) * p.kv_heads * ((max_vlen + tile - 1) / tile);
+    if (tiles >= (1ll << 30)) { *why = "more than 2^30 tiles"; return false; }
     int64_t ctas;
     if (p.num_ctas > 0) {
         ctas = std::min<int64_t>(p.num_ctas, kMaxCtas);
@@ -229,7 +236,8 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
 {
     Problem &p = plan->problem;
     p.sm_count = device_sm_count();
-    if (p.sm_count <= 0) return fail(SA_ERR_DEVICE, "no CUDA device is current");
+    if (p.sm_count <= 0 || cudaGetDevice(&plan->device) != cudaSuccess)
+        return fail(SA_ERR_DEVICE, "no CUDA device is current");
     if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(SA_ERR_INVALID, "workspace must be 16-byte aligned");
     const size_t head = kStatusWords * 4 + counters_bytes(p.batch, p.q_heads);
     if (workspace_bytes < head) return fail(SA_ERR_INVALID, "workspace too small");
@@ -675,7 +683,14 @@ sa_plan_t *sa_seed_plan_create(const void *q, const void *k, const void *v, void
 int sa_plan_run(const sa_plan_t *plan, sa_stream_t stream)
 {
     if (!plan) return fail(SA_ERR_INVALID, "null plan");
-    return run_plan(plan, static_cast<cudaStream_t>(stream));
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess) return fail(SA_ERR_DEVICE, "no CUDA device is current");
+    if (current == plan->device) return run_plan(plan, static_cast<cudaStream_t>(stream));
+    // The plan's buffers live on another device than the caller's current one: switch for the launch.
+    if (cudaSetDevice(plan->device) != cudaSuccess) return fail(SA_ERR_DEVICE, "cannot select the plan's device");
+    const int rc = run_plan(plan, static_cast<cudaStream_t>(stream));
+    cudaSetDevice(current);
+    return rc;
 }
 
 int sa_plan_kernel(const sa_plan_t *plan) { return plan ? (plan->use_stream ? SA_KERNEL_STREAM : SA_KERNEL_GENERIC) : 0; }

@@ -19,6 +19,10 @@
 
 namespace sa {
 
+#ifdef SA_TIMELINE
+extern unsigned long long *g_timeline;
+#endif
+
 namespace {
 
 constexpr int kTileBytes = 8192;             // one K or one V tile
@@ -42,7 +46,16 @@ struct StreamParams {
     int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
     SeqDesc seq;
+#ifdef SA_TIMELINE
+    unsigned long long *timeline;  // debug builds only: 8 globaltimer stamps per CTA
+#endif
 };
+
+#ifdef SA_TIMELINE
+#define SA_STAMP(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
+#else
+#define SA_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -159,6 +172,15 @@ template <> struct Mma<__half> {
     }
 };
 
+// One fragment (TMA box) of a tile as seen by the issuing lane.
+struct Frag {
+    int state;          // 0: nothing to load, 1: load, 2: page id out of range (skip + report)
+    int tok;            // token coordinate of the box
+    int outer;          // outermost coordinate: batch row or physical page
+    int kvh;            // kv head coordinate
+    int64_t trace_idx;  // slot of the page-walk trace to record, or -1
+};
+
 template <typename T, int D, int WARPS, int STAGES, bool ROWS16>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -171,13 +193,18 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     constexpr int KS_QK = D / 16;      // k-steps of q.k
     constexpr int NT_O = D / 8;        // output n-tiles (8 columns each)
     constexpr int KS_PV = TILE_N / 16; // k-steps of p.v
-    constexpr int STATE_STRIDE = D + 2;
+    constexpr int ROWS = ROWS16 ? 16 : 8;
+    constexpr int STATE_STRIDE = D + 2;  // (o[D], m, l): shared-memory states and the SA_OUT_STATE output
+    constexpr int PART_STRIDE = D + 4;   // split states in the workspace: padded to 16-byte rows
+    constexpr int STATE_FLOATS = ROWS * STATE_STRIDE;  // one warp's (o, m, l) rows
     constexpr int NTHREADS = WARPS * 32;
+    constexpr int BAR_BYTES = (WARPS * STAGES * 8 + 15) / 16 * 16;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + WARPS * STAGES * kStageBytes);
-    int *prefix = reinterpret_cast<int *>(bars + WARPS * STAGES);
+    float *states = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + BAR_BYTES);
+    int *prefix = reinterpret_cast<int *>(states + WARPS * STATE_FLOATS);
     __shared__ int s_last;
 
     const int tid = threadIdx.x;
@@ -188,43 +215,145 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int C = gridDim.x;
     const int c = blockIdx.x;
     const int group = p.group;
+    const int Hkv = p.kv_heads;
     const bool ragged = p.uniform_tiles < 0;
 
     const uint32_t ring_u32 = smem_u32(ring) + warp * STAGES * kStageBytes;
     const uint32_t bar_u32 = smem_u32(bars) + warp * STAGES * 8;
     uint8_t *warp_ring = ring + warp * STAGES * kStageBytes;
 
+    SA_STAMP(0);
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_v)) : "memory");
+    }
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (ragged && warp == 0) {
-        int running = 0;
-        for (int base = 0; base < p.batch; base += 32) {
-            const int b = base + lane;
-            int x = 0;
-            if (b < p.batch) x = static_cast<int>((row_vlen(p.seq, b) + TILE_N - 1) / TILE_N);
+    if (ragged) {
+        // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
+        if (warp == 0) {
+            int running = 0;
+            for (int base = 0; base < p.batch; base += 32) {
+                const int b = base + lane;
+                int x = 0;
+                if (b < p.batch) x = static_cast<int>((row_vlen(p.seq, b) + TILE_N - 1) / TILE_N);
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int y = __shfl_up_sync(0xffffffffu, x, o);
-                if (lane >= o) x += y;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int y = __shfl_up_sync(0xffffffffu, x, o);
+                    if (lane >= o) x += y;
+                }
+                if (b < p.batch) prefix[b + 1] = running + x;
+                running += __shfl_sync(0xffffffffu, x, 31);
             }
-            if (b < p.batch) prefix[b + 1] = running + x;
-            running += __shfl_sync(0xffffffffu, x, 31);
+            if (lane == 0) prefix[0] = 0;
         }
-        if (lane == 0) prefix[0] = 0;
+        __syncthreads();
+    } else {
+        __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
     }
     fence_proxy_async();
-    __syncthreads();
 
     const uint64_t policy = make_evict_first_policy();
-    const int Hkv = p.kv_heads;
-    auto tiles_before = [&](int b) -> int64_t {
-        return ragged ? static_cast<int64_t>(prefix[b]) : static_cast<int64_t>(b) * p.uniform_tiles;
+    // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
+    // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
+    auto tiles_before = [&](int b) -> int { return ragged ? prefix[b] : b * p.uniform_tiles; };
+    const int total_tiles = Hkv * tiles_before(p.batch);
+    auto owner = [&](int x) -> int {
+        return static_cast<int>(((static_cast<int64_t>(x) + 1) * C - 1) / total_tiles);
     };
-    const int64_t total_tiles = static_cast<int64_t>(Hkv) * tiles_before(p.batch);
-    auto owner = [&](int64_t x) -> int64_t { return ((x + 1) * C - 1) / total_tiles; };
+    // Global tile x -> (row, kv head, first global tile of the pair, tiles per row).
+    auto locate = [&](int x, int &b, int &kvh, int &row_tiles, int &pair_start) {
+        if (ragged) {
+            int lo_b = 0, hi_b = p.batch;  // largest b with Hkv*prefix[b] <= x
+            while (hi_b - lo_b > 1) {
+                const int mid = (lo_b + hi_b) >> 1;
+                if (Hkv * prefix[mid] <= x) lo_b = mid; else hi_b = mid;
+            }
+            b = lo_b;
+        } else {
+            b = static_cast<int>(static_cast<unsigned>(x) / static_cast<unsigned>(Hkv * p.uniform_tiles));
+        }
+        row_tiles = tiles_before(b + 1) - tiles_before(b);
+        const int row_start = Hkv * tiles_before(b);
+        kvh = static_cast<int>(static_cast<unsigned>(x - row_start) / static_cast<unsigned>(row_tiles));
+        pair_start = row_start + kvh * row_tiles;
+    };
+
+    const int lo = total_tiles > 0 ? static_cast<int>(static_cast<int64_t>(total_tiles) * c / C) : 0;
+    const int hi = total_tiles > 0 ? static_cast<int>(static_cast<int64_t>(total_tiles) * (c + 1) / C) : 0;
+    // This warp's tiles are lo + warp + j*WARPS for j in [0, n_w), across all segments of the CTA,
+    // so its copy pipeline keeps running through segment boundaries.
+    const int n_w = hi - lo > warp ? (hi - lo - warp + WARPS - 1) / WARPS : 0;
+
+    // What this lane has to copy for the warp's j-th tile (page-table lookups happen here, one
+    // tile before the copies are issued, so their latency stays off the critical path).
+    auto lookup = [&](int j) -> Frag {
+        Frag f;
+        f.state = 0; f.tok = 0; f.outer = 0; f.kvh = 0; f.trace_idx = -1;
+        if (j >= n_w || lane >= p.frags_per_tile) return f;
+        int b, kvh, row_tiles, pair_start;
+        const int x = lo + warp + j * WARPS;
+        locate(x, b, kvh, row_tiles, pair_start);
+        f.kvh = kvh;
+        const unsigned vfrag = static_cast<unsigned>(x - pair_start) * p.frags_per_tile + lane;
+        const int64_t vtok0 = static_cast<int64_t>(vfrag) * p.frag_tokens;
+        if (vtok0 >= row_vlen(p.seq, b)) return f;
+        if (p.seq.mode == kContig) {
+            f.tok = static_cast<int>(vtok0);
+            f.outer = b;
+            f.state = 1;
+        } else if (p.seq.mode == kPaged) {
+            const unsigned lp = vfrag / static_cast<unsigned>(p.frags_per_unit);
+            const int sub = static_cast<int>(vfrag - lp * p.frags_per_unit);
+            const int64_t slot = static_cast<int64_t>(b) * p.seq.max_pages + lp;
+            const int64_t page = load_index(p.seq.page_table, p.seq.table_i64, slot);
+            f.tok = sub * p.frag_tokens;
+            f.outer = static_cast<int>(page);
+            f.state = (page >= 0 && page < p.seq.num_pages) ? 1 : 2;
+            if (kvh == 0 && sub == 0) f.trace_idx = slot;
+        } else {
+            const unsigned bi = vfrag / static_cast<unsigned>(p.frags_per_unit);
+            const int sub = static_cast<int>(vfrag - bi * p.frags_per_unit);
+            f.tok = p.seq.blocks[bi] * p.seq.block_size + sub * p.frag_tokens;
+            f.outer = b;
+            f.state = 1;
+        }
+        return f;
+    };
+
+    // Issue the TMA copies of the warp's j-th tile into ring slot j % STAGES.
+    auto issue = [&](int j, const Frag &f) {
+        const uint32_t slot = static_cast<uint32_t>(j) % STAGES;
+        const uint32_t stage = ring_u32 + slot * kStageBytes;
+        const uint32_t bar = bar_u32 + slot * 8;
+        const bool ok = f.state == 1;
+        if (f.state == 2) atomicOr(p.status, SA_DEV_BAD_PAGE);
+        if (ok && p.trace != nullptr && f.trace_idx >= 0) p.trace[f.trace_idx] = static_cast<int32_t>(f.outer);
+        const unsigned mask = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0)
+            mbar_arrive_expect_tx(bar, static_cast<uint32_t>(__popc(mask)) * p.frag_tokens * 128 * HALVES * 2);
+        __syncwarp();
+        if (ok) {
+            const uint32_t dst = stage + lane * p.frag_tokens * 128;
+            const int c1 = p.tok_dim == 1 ? f.tok : f.kvh;
+            const int c2 = p.tok_dim == 1 ? f.kvh : f.tok;
+#pragma unroll
+            for (int hf = 0; hf < HALVES; ++hf) {
+                tma_load_4d(dst + hf * HALF_BYTES, &tm_k, bar, hf * 64, c1, c2, f.outer, policy);
+                tma_load_4d(dst + kTileBytes + hf * HALF_BYTES, &tm_v, bar, hf * 64, c1, c2, f.outer, policy);
+            }
+        }
+    };
+
+    // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s)
+        if (s < n_w) issue(s, lookup(s));
+    Frag pending = lookup(STAGES);
+    SA_STAMP(1);
 
     // Rows with no tokens are not part of the tile list: write their (empty) result here.
     for (int b = c; b < p.batch; b += C) {
@@ -245,33 +374,16 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
     }
 
-    if (total_tiles == 0) return;
-    const int64_t lo = total_tiles * c / C;
-    const int64_t hi = total_tiles * (c + 1) / C;
-    int64_t cur = lo;
-    uint32_t tile_base = 0;  // tiles this warp has pushed through its ring so far
-    bool dead = false;       // a bounded wait gave up: stop computing, keep the barriers
+    int cur = lo;
+    int j = 0;          // next tile of this warp to consume
+    bool dead = false;  // a bounded wait gave up: stop computing, keep the CTA barriers
 
     while (cur < hi) {
-        // Locate the (row, kv head) pair that owns global tile `cur`.
-        int b;
-        if (ragged) {
-            int lo_b = 0, hi_b = p.batch;  // largest b with Hkv*prefix[b] <= cur
-            while (hi_b - lo_b > 1) {
-                const int mid = (lo_b + hi_b) >> 1;
-                if (static_cast<int64_t>(Hkv) * prefix[mid] <= cur) lo_b = mid; else hi_b = mid;
-            }
-            b = lo_b;
-        } else {
-            b = static_cast<int>(cur / (static_cast<int64_t>(Hkv) * p.uniform_tiles));
-        }
-        const int row_tiles = static_cast<int>(tiles_before(b + 1) - tiles_before(b));
-        const int64_t row_start = static_cast<int64_t>(Hkv) * tiles_before(b);
-        const int kvh = static_cast<int>((cur - row_start) / row_tiles);
-        const int64_t pair_start = row_start + static_cast<int64_t>(kvh) * row_tiles;
-        const int64_t pair_end = pair_start + row_tiles;
-        const int seg_lo = static_cast<int>(cur - pair_start);
-        const int seg_hi = static_cast<int>((hi < pair_end ? hi : pair_end) - pair_start);
+        // The segment: tiles [cur, seg_end) of one (row, kv head) pair.
+        int b, kvh, row_tiles, pair_start;
+        locate(cur, b, kvh, row_tiles, pair_start);
+        const int pair_end = pair_start + row_tiles;
+        const int seg_end = hi < pair_end ? hi : pair_end;
         const int pair = b * Hkv + kvh;
         const int64_t vlen = row_vlen(p.seq, b);
 
@@ -292,66 +404,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
 
-        const int seg_tiles = seg_hi - seg_lo;
-        const int n_w = seg_tiles > warp ? (seg_tiles - warp + WARPS - 1) / WARPS : 0;
-
-        // Issue the TMA copies of this warp's j-th tile of the segment.
-        auto issue = [&](int j) {
-            const int lt = seg_lo + warp + j * WARPS;
-            const uint32_t slot = (tile_base + j) % STAGES;
-            const uint32_t stage = ring_u32 + slot * kStageBytes;
-            const uint32_t bar = bar_u32 + slot * 8;
-            bool valid = false;
-            int tok = 0, outer = 0;
-            if (lane < p.frags_per_tile) {
-                const int64_t vfrag = static_cast<int64_t>(lt) * p.frags_per_tile + lane;
-                const int64_t vtok0 = vfrag * p.frag_tokens;
-                valid = vtok0 < vlen;
-                if (valid) {
-                    if (p.seq.mode == kContig) {
-                        tok = static_cast<int>(vtok0);
-                        outer = b;
-                    } else if (p.seq.mode == kPaged) {
-                        const int64_t lp = vfrag / p.frags_per_unit;
-                        const int sub = static_cast<int>(vfrag % p.frags_per_unit);
-                        const int64_t page =
-                            load_index(p.seq.page_table, p.seq.table_i64, static_cast<int64_t>(b) * p.seq.max_pages + lp);
-                        if (page < 0 || page >= p.seq.num_pages) {
-                            valid = false;
-                            atomicOr(p.status, SA_DEV_BAD_PAGE);
-                        } else {
-                            tok = sub * p.frag_tokens;
-                            outer = static_cast<int>(page);
-                            if (p.trace != nullptr && kvh == 0 && sub == 0)
-                                p.trace[static_cast<int64_t>(b) * p.seq.max_pages + lp] = static_cast<int32_t>(page);
-                        }
-                    } else {
-                        const int blk = p.seq.blocks[vfrag / p.frags_per_unit];
-                        const int sub = static_cast<int>(vfrag % p.frags_per_unit);
-                        tok = blk * p.seq.block_size + sub * p.frag_tokens;
-                        outer = b;
-                    }
-                }
-            }
-            const unsigned mask = __ballot_sync(0xffffffffu, valid);
-            if (lane == 0)
-                mbar_arrive_expect_tx(bar, static_cast<uint32_t>(__popc(mask)) * p.frag_tokens * 128 * HALVES * 2);
-            __syncwarp();
-            if (valid) {
-                const uint32_t dst = stage + lane * p.frag_tokens * 128;
-                const int c1 = p.tok_dim == 1 ? tok : kvh;
-                const int c2 = p.tok_dim == 1 ? kvh : tok;
-#pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf) {
-                    tma_load_4d(dst + hf * HALF_BYTES, &tm_k, bar, hf * 64, c1, c2, outer, policy);
-                    tma_load_4d(dst + kTileBytes + hf * HALF_BYTES, &tm_v, bar, hf * 64, c1, c2, outer, policy);
-                }
-            }
-        };
-
-        const int prologue = n_w < STAGES ? n_w : STAGES;
-        for (int j = 0; j < prologue; ++j) issue(j);
-
         float m_run[2] = {-INFINITY, -INFINITY};
         float l_run[2] = {0.0f, 0.0f};
         float o_acc[NT_O][4];
@@ -363,10 +415,12 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             o_acc[i][3] = 0.0f;
         }
 
-        for (int j = 0; j < n_w; ++j) {
-            const int lt = seg_lo + warp + j * WARPS;
-            const uint32_t slot = (tile_base + j) % STAGES;
-            const uint32_t parity = ((tile_base + j) / STAGES) & 1u;
+        for (; j < n_w; ++j) {
+            const int x = lo + warp + j * WARPS;
+            if (x >= seg_end) break;
+            const int lt = x - pair_start;
+            const uint32_t slot = static_cast<uint32_t>(j) % STAGES;
+            const uint32_t parity = (static_cast<uint32_t>(j) / STAGES) & 1u;
             const uint32_t kb = ring_u32 + slot * kStageBytes;
             const uint32_t vb = kb + kTileBytes;
             if (!dead && !mbar_wait(bar_u32 + slot * 8, parity)) {
@@ -375,6 +429,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
             dead = __any_sync(0xffffffffu, dead);
             if (dead) continue;
+            if (j == 0) SA_STAMP(2);
 
             const int64_t tile_tok0 = static_cast<int64_t>(lt) * TILE_N;
             const int n_valid = vlen - tile_tok0 < TILE_N ? static_cast<int>(vlen - tile_tok0) : TILE_N;
@@ -502,11 +557,12 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             // Order this warp's shared-memory accesses before the async-proxy writes of the refill.
             fence_proxy_async();
             __syncwarp();
-            if (j + STAGES < n_w) issue(j + STAGES);
+            if (j + STAGES < n_w) issue(j + STAGES, pending);
+            pending = lookup(j + STAGES + 1);
         }
-        tile_base += n_w;
 
-        // Warp state -> this warp's (now idle) ring memory: [ROWS][D+2] floats = (o, m, l).
+        SA_STAMP(3);
+        // Warp state -> the warp's state area: [ROWS][D+2] floats = (o, m, l).
         {
             l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
             l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
@@ -514,7 +570,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
                 l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
             }
-            float *area = reinterpret_cast<float *>(warp_ring);
+            float *area = states + warp * STATE_FLOATS;
 #pragma unroll
             for (int i = 0; i < NT_O; ++i) {
                 const int d = i * 8 + 2 * t4;
@@ -533,41 +589,55 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
         __syncthreads();
+        SA_STAMP(4);
 
         // Combine the warps of this CTA, then either finish the pair or publish a state.
-        const int64_t first_cta = owner(pair_start);
-        const int nseg = static_cast<int>(owner(pair_end - 1) - first_cta) + 1;
-        const int64_t slot_stride = static_cast<int64_t>(group) * STATE_STRIDE;
+        // Work items are 4 consecutive columns of one head row.
+        const int first_cta = owner(pair_start);
+        const int nseg = owner(pair_end - 1) - first_cta + 1;
+        const int64_t slot_stride = static_cast<int64_t>(group) * PART_STRIDE;
         float *my_slot = p.partials + (static_cast<int64_t>(c) + pair) * slot_stride;
         const int64_t out_row0 = static_cast<int64_t>(b) * p.q_heads + static_cast<int64_t>(kvh) * group;
-        for (int idx = tid; idx < group * D; idx += NTHREADS) {
-            const int row = idx / D;
-            const int d = idx - row * D;
+        auto store_result = [&](int row, int d4, const float4 &acc, float big, float total_l) {
+            if (p.out_mode == SA_OUT_FINAL) {
+                const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
+                T *dst = static_cast<T *>(p.out) + (out_row0 + row) * D + d4;
+                *reinterpret_cast<uint2 *>(dst) =
+                    make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
+            } else {
+                float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
+                *reinterpret_cast<float2 *>(dst + d4) = make_float2(acc.x, acc.y);
+                *reinterpret_cast<float2 *>(dst + d4 + 2) = make_float2(acc.z, acc.w);
+                if (d4 == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(big, total_l);
+            }
+        };
+        const int items = group * (D / 4);
+        for (int item = tid; item < items; item += NTHREADS) {
+            const int row = item / (D / 4);
+            const int d4 = (item - row * (D / 4)) * 4;
             float big = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) {
-                const float *area = reinterpret_cast<const float *>(ring + w * STAGES * kStageBytes);
-                big = fmaxf(big, area[row * STATE_STRIDE + D]);
-            }
-            float acc = 0.0f, total_l = 0.0f;
+            for (int w = 0; w < WARPS; ++w) big = fmaxf(big, states[w * STATE_FLOATS + row * STATE_STRIDE + D]);
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float total_l = 0.0f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) {
-                const float *area = reinterpret_cast<const float *>(ring + w * STAGES * kStageBytes);
-                const float wgt = exp2_diff(area[row * STATE_STRIDE + D], big);
-                acc += wgt * area[row * STATE_STRIDE + d];
-                total_l += wgt * area[row * STATE_STRIDE + D + 1];
+                const float *area = states + w * STATE_FLOATS + row * STATE_STRIDE;
+                const float wgt = exp2_diff(area[D], big);
+                const float2 lo2 = *reinterpret_cast<const float2 *>(area + d4);
+                const float2 hi2 = *reinterpret_cast<const float2 *>(area + d4 + 2);
+                acc.x += wgt * lo2.x;
+                acc.y += wgt * lo2.y;
+                acc.z += wgt * hi2.x;
+                acc.w += wgt * hi2.y;
+                total_l += wgt * area[D + 1];
             }
-            if (nseg == 1 && p.out_mode == SA_OUT_FINAL) {
-                static_cast<T *>(p.out)[(out_row0 + row) * D + d] =
-                    Elem<T>::from_float(total_l > 0.0f ? acc / total_l : 0.0f);
+            if (nseg == 1) {
+                store_result(row, d4, acc, big, total_l);
             } else {
-                float *dst = nseg == 1 ? static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE
-                                       : my_slot + row * STATE_STRIDE;
-                dst[d] = acc;
-                if (d == 0) {
-                    dst[D] = big;
-                    dst[D + 1] = total_l;
-                }
+                float *dst = my_slot + row * PART_STRIDE;
+                *reinterpret_cast<float4 *>(dst + d4) = acc;
+                if (d4 == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(big, total_l);
             }
         }
 
@@ -576,40 +646,68 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             __syncthreads();
             if (tid == 0) s_last = atomicAdd(p.counters + pair, 1) == nseg - 1;
             __syncthreads();
+            SA_STAMP(5);
             if (s_last) {
+                // Last CTA to arrive on this pair: exact merge of its nseg split states.  All loads
+                // are issued before they are needed (the states sit in L2, ~1 us away).
                 __threadfence();
-                const float *first_slot = p.partials + (first_cta + pair) * slot_stride;
-                for (int idx = tid; idx < group * D; idx += NTHREADS) {
-                    const int row = idx / D;
-                    const int d = idx - row * D;
+                const float *first_slot = p.partials + (static_cast<int64_t>(first_cta) + pair) * slot_stride;
+                constexpr int CAP = WARPS * STATE_FLOATS / 2;
+                float *sm_m = states;        // the state areas are free again: reuse them for (m, l)
+                float *sm_l = states + CAP;
+                const bool staged = group * nseg <= CAP;
+                if (staged) {
+                    for (int t = tid; t < group * nseg; t += NTHREADS) {
+                        const int i = t / group;
+                        const int row = t - i * group;
+                        const float2 ml = __ldcg(
+                            reinterpret_cast<const float2 *>(first_slot + i * slot_stride + row * PART_STRIDE + D));
+                        sm_m[row * nseg + i] = ml.x;
+                        sm_l[row * nseg + i] = ml.y;
+                    }
+                    __syncthreads();
+                }
+                for (int item = tid; item < items; item += NTHREADS) {
+                    const int row = item / (D / 4);
+                    const int d4 = (item - row * (D / 4)) * 4;
+                    const float *row_state = first_slot + row * PART_STRIDE;
                     float big = -INFINITY;
-                    for (int i = 0; i < nseg; ++i)
-                        big = fmaxf(big, __ldcg(first_slot + i * slot_stride + row * STATE_STRIDE + D));
-                    float acc = 0.0f, total_l = 0.0f;
-                    for (int i = 0; i < nseg; ++i) {
-                        const float *st = first_slot + i * slot_stride + row * STATE_STRIDE;
-                        const float wgt = exp2_diff(__ldcg(st + D), big);
-                        acc += wgt * __ldcg(st + d);
-                        total_l += wgt * __ldcg(st + D + 1);
-                    }
-                    if (p.out_mode == SA_OUT_FINAL) {
-                        static_cast<T *>(p.out)[(out_row0 + row) * D + d] =
-                            Elem<T>::from_float(total_l > 0.0f ? acc / total_l : 0.0f);
+                    if (staged) {
+                        for (int i = 0; i < nseg; ++i) big = fmaxf(big, sm_m[row * nseg + i]);
                     } else {
-                        float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
-                        dst[d] = acc;
-                        if (d == 0) {
-                            dst[D] = big;
-                            dst[D + 1] = total_l;
-                        }
+#pragma unroll 4
+                        for (int i = 0; i < nseg; ++i) big = fmaxf(big, __ldcg(row_state + i * slot_stride + D));
                     }
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    float total_l = 0.0f;
+#pragma unroll 8
+                    for (int i = 0; i < nseg; ++i) {
+                        const float *st = row_state + i * slot_stride;
+                        const float4 o = __ldcg(reinterpret_cast<const float4 *>(st + d4));
+                        float mi, li;
+                        if (staged) {
+                            mi = sm_m[row * nseg + i];
+                            li = sm_l[row * nseg + i];
+                        } else {
+                            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(st + D));
+                            mi = ml.x;
+                            li = ml.y;
+                        }
+                        const float wgt = exp2_diff(mi, big);
+                        acc.x += wgt * o.x;
+                        acc.y += wgt * o.y;
+                        acc.z += wgt * o.z;
+                        acc.w += wgt * o.w;
+                        total_l += wgt * li;
+                    }
+                    store_result(row, d4, acc, big, total_l);
                 }
                 if (tid == 0) p.counters[pair] = 0;  // ready for the next launch
             }
         }
-        fence_proxy_async();
-        __syncthreads();  // ring memory and s_last are reused by the next segment
-        cur = pair_start + seg_hi;
+        __syncthreads();  // the state areas and s_last are reused by the next segment
+        SA_STAMP(6);
+        cur = seg_end;
     }
 }
 
@@ -623,8 +721,7 @@ cudaError_t launch_instance(const CUtensorMap &mk, const CUtensorMap &mv, const 
                             int batch, cudaStream_t stream)
 {
     auto kernel = stream_decode_kernel<T, D, WARPS, STAGES, ROWS16>;
-    const size_t smem = 1024 + static_cast<size_t>(WARPS) * STAGES * kStageBytes + WARPS * STAGES * 8 +
-                        (static_cast<size_t>(batch) + 1) * 4 + 16;
+    const size_t smem = stream_smem_bytes(D, ROWS16, STAGES, batch);
     // Opt in to the dynamic shared memory this launch needs (grows only; per device).
     static std::mutex mu;
     static size_t configured[64] = {};
@@ -648,13 +745,35 @@ template <typename T, int D>
 cudaError_t launch_dim(const CUtensorMap &mk, const CUtensorMap &mv, const StreamParams &sp, int ctas, int batch,
                        bool rows16, cudaStream_t stream)
 {
-    if (rows16) return launch_instance<T, D, kStreamWarps, kStreamStages, true>(mk, mv, sp, ctas, batch, stream);
+    if (rows16) {
+        // 16 head rows at D128 need 33 KB of state areas: two ring stages instead of three.
+        constexpr int kStages16 = D == 128 ? 2 : kStreamStages;
+        return launch_instance<T, D, kStreamWarps, kStages16, true>(mk, mv, sp, ctas, batch, stream);
+    }
     return launch_instance<T, D, kStreamWarps, kStreamStages, false>(mk, mv, sp, ctas, batch, stream);
 }
 
 }  // namespace
 
+#ifdef SA_TIMELINE
+unsigned long long *g_timeline = nullptr;
+extern "C" __attribute__((visibility("default"))) void sa_debug_timeline(void *ptr)
+{
+    g_timeline = static_cast<unsigned long long *>(ptr);
+}
+#endif
+
 int stream_tile_tokens(int head_dim) { return kTileBytes / (head_dim * 2); }
+
+int stream_stages(int head_dim, bool rows16) { return (head_dim == 128 && rows16) ? 2 : kStreamStages; }
+
+size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch)
+{
+    const size_t bars = (static_cast<size_t>(kStreamWarps) * stages * 8 + 15) / 16 * 16;
+    const size_t states = static_cast<size_t>(kStreamWarps) * (rows16 ? 16 : 8) * (head_dim + 2) * 4;
+    return 1024 + static_cast<size_t>(kStreamWarps) * stages * kStageBytes + bars + states +
+           (static_cast<size_t>(batch) + 1) * 4 + 16;
+}
 
 cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream)
 {
@@ -679,6 +798,9 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStrea
     sp.tok_dim = geo.tok_dim;
     sp.uniform_tiles = geo.uniform_tiles;
     sp.seq = p.seq;
+#ifdef SA_TIMELINE
+    sp.timeline = g_timeline;
+#endif
     const bool rows16 = sp.group > 8;
     if (p.dtype == SA_DTYPE_BF16) {
         if (p.head_dim == 64)

@@ -20,6 +20,9 @@ struct StreamGeometry {
 };
 
 int stream_tile_tokens(int head_dim);
+int stream_stages(int head_dim, bool rows16);
+size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch);
+constexpr size_t kStreamSmemLimit = 227 * 1024 - 64;
 cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream);
 
 }  // namespace sa

@@ -150,8 +150,15 @@ def device_supported(device: torch.device) -> bool:
     return bool(load().sa_device_supported(int(index)))
 
 
+_current_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+if _current_raw_stream is None:  # older torch: go through the Stream object
+    def _current_raw_stream(index: int) -> int:
+        return int(torch.cuda.current_stream(index).cuda_stream)
+
+
 def stream_handle(device: torch.device) -> int:
-    return int(torch.cuda.current_stream(device).cuda_stream)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return int(_current_raw_stream(index))
 
 
 def workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int, num_ctas: int = 0) -> int:
@@ -221,11 +228,8 @@ class NativePlan:
         self.launches = int(lib.sa_plan_launches(self._handle))
 
     def run(self) -> None:
-        if torch.cuda.current_device() != self._device_index:
-            with torch.cuda.device(self._device_index):
-                rc = self._run(self._handle, torch.cuda.current_stream().cuda_stream)
-        else:
-            rc = self._run(self._handle, torch.cuda.current_stream().cuda_stream)
+        # Raw handle of the device's current stream; the library selects the plan's device itself.
+        rc = self._run(self._handle, _current_raw_stream(self._device_index))
         if rc:
             check(rc)
 
