@@ -5,9 +5,9 @@
 // on the tensor cores (m16n8k16, query heads of one KV group on the M rows, fp32
 // accumulation) with a single-pass online softmax in the base-2 domain.
 //
-// Work is a flat list of tiles over all (row, kv head) pairs; CTA c takes the
-// contiguous slice [T*c/C, T*(c+1)/C), so ragged rows are balanced by tokens and
-// a pair may be covered by several CTAs.  Each covering CTA writes an (m, l, o)
+// Work is a flat list of tiles over all (row, kv head) pairs, split over the CTAs in
+// contiguous slices (balanced by tokens, so ragged rows cost what they hold); a pair
+// is usually covered by several CTAs.  Each covering CTA writes an (m, l, o)
 // state; the last one to arrive (atomic ticket, no waiting) merges them exactly
 // and writes the output, so one launch does producer and merge.
 //
@@ -43,6 +43,9 @@ struct StreamParams {
     int frag_tokens;     // rows of one TMA box
     int frags_per_tile;  // TILE_N / frag_tokens
     int frags_per_unit;  // fragments per page / seed block (>= 1)
+    int frag_shift;      // log2(frag_tokens)
+    int fpt_shift;       // log2(frags_per_tile)
+    int fpu_shift;       // log2(frags_per_unit)
     int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
     SeqDesc seq;
@@ -52,9 +55,18 @@ struct StreamParams {
 };
 
 #ifdef SA_TIMELINE
-#define SA_STAMP(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
+#define SA_STAMP_RAW(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
+#if SA_TIMELINE == 2
+#define SA_PSTAMP(i) SA_STAMP_RAW(i)
+#define SA_STAMP(i) do { if ((i) < 2) SA_STAMP_RAW(i); } while (0)
+#else
+#define SA_STAMP(i) SA_STAMP_RAW(i)
+#endif
 #else
 #define SA_STAMP(i) do { } while (0)
+#endif
+#ifndef SA_PSTAMP
+#define SA_PSTAMP(i) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -255,14 +267,22 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
     }
     fence_proxy_async();
+    SA_PSTAMP(2);
 
     const uint64_t policy = make_evict_first_policy();
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
     // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
     auto tiles_before = [&](int b) -> int { return ragged ? prefix[b] : b * p.uniform_tiles; };
     const int total_tiles = Hkv * tiles_before(p.batch);
+    // CTA c owns tiles [c*q + min(c, r), (c+1)*q + min(c+1, r)) with q = T / C, r = T % C:
+    // the first r CTAs take one extra tile.  owner(x) is the CTA that owns tile x.
+    const unsigned q_t = static_cast<unsigned>(total_tiles) / static_cast<unsigned>(C);
+    const unsigned r_t = static_cast<unsigned>(total_tiles) - q_t * C;
+    auto range_lo = [&](unsigned cc) -> int { return static_cast<int>(cc * q_t + (cc < r_t ? cc : r_t)); };
     auto owner = [&](int x) -> int {
-        return static_cast<int>(((static_cast<int64_t>(x) + 1) * C - 1) / total_tiles);
+        const unsigned ux = static_cast<unsigned>(x);
+        const unsigned wide = r_t * (q_t + 1);  // tiles held by the CTAs that take q+1
+        return static_cast<int>(ux < wide ? ux / (q_t + 1) : r_t + (ux - wide) / q_t);
     };
     // Global tile x -> (row, kv head, first global tile of the pair, tiles per row).
     auto locate = [&](int x, int &b, int &kvh, int &row_tiles, int &pair_start) {
@@ -282,43 +302,147 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         pair_start = row_start + kvh * row_tiles;
     };
 
-    const int lo = total_tiles > 0 ? static_cast<int>(static_cast<int64_t>(total_tiles) * c / C) : 0;
-    const int hi = total_tiles > 0 ? static_cast<int>(static_cast<int64_t>(total_tiles) * (c + 1) / C) : 0;
+    // Partition of the tile list over the CTAs.  A segment boundary inside a CTA stalls its four
+    // warps for the flush/combine, so when there are at least four CTAs per (row, kv head) pair
+    // the slice boundaries are snapped to pair boundaries ("aligned"): pair p gets the CTAs
+    // [cs(p), cs(p+1)) with cs(p) = round(C * tiles_before_pair(p) / T), and splits its tiles
+    // evenly among them; every CTA then has exactly one segment.  Otherwise the flat rule is used.
+    const int num_pairs = p.batch * Hkv;
+    int lo = 0, hi = 0;
+    int al_first = 0, al_nseg = 0;
+    bool aligned = total_tiles > 0 && 4 * num_pairs <= C &&
+                   static_cast<uint64_t>(C) * static_cast<uint64_t>(total_tiles) < (1ull << 32);
+    int al_pair = -1, al_start = 0, al_end = 0;  // aligned mode: this CTA's pair and its tile range
+    if (aligned) {
+        // One pair per lane: lane pp computes cs(pp); cs(pp+1) comes from the neighbour lane.
+        const unsigned half = static_cast<unsigned>(total_tiles) / 2;
+        bool ok = true;
+        int s0 = 0, s1 = 0;
+        unsigned t0 = 0, t1 = 0;
+        for (int base = 0; base < num_pairs && al_pair < 0; base += 31) {
+            const int pp = base + lane;  // lanes 0..30 own a pair, lane 31 only supplies cs(pp) to lane 30
+            unsigned before = static_cast<unsigned>(total_tiles);
+            if (pp < num_pairs) {
+                const int bb = pp / Hkv;
+                const int tb = tiles_before(bb);
+                before = static_cast<unsigned>(Hkv * tb + (pp - bb * Hkv) * (tiles_before(bb + 1) - tb));
+            }
+            const int start = static_cast<int>((static_cast<unsigned>(C) * before + half) /
+                                               static_cast<unsigned>(total_tiles));
+            const int next_start = __shfl_down_sync(0xffffffffu, start, 1);
+            const unsigned next_before = __shfl_down_sync(0xffffffffu, before, 1);
+            const bool owns = lane < 31 && pp < num_pairs;
+            if (owns && next_before > before && next_start <= start) ok = false;
+            const bool hit = owns && c >= start && c < next_start;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (m != 0u) {
+                const int src = __ffs(m) - 1;
+                al_pair = base + src;
+                s0 = __shfl_sync(0xffffffffu, start, src);
+                s1 = __shfl_sync(0xffffffffu, next_start, src);
+                t0 = __shfl_sync(0xffffffffu, before, src);
+                t1 = __shfl_sync(0xffffffffu, next_before, src);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+        }
+        // The "every pair with tiles gets a CTA" test must cover all pairs even after the hit.
+        if (ok && num_pairs > 31) {
+            for (int base = 0; base < num_pairs; base += 32) {
+                const int pp = base + lane;
+                if (pp < num_pairs) {
+                    auto before_of = [&](int q) -> unsigned {
+                        if (q >= num_pairs) return static_cast<unsigned>(total_tiles);
+                        const int bb = q / Hkv;
+                        const int tb = tiles_before(bb);
+                        return static_cast<unsigned>(Hkv * tb + (q - bb * Hkv) * (tiles_before(bb + 1) - tb));
+                    };
+                    const unsigned b0 = before_of(pp), b1 = before_of(pp + 1);
+                    const unsigned c0 = (static_cast<unsigned>(C) * b0 + half) / static_cast<unsigned>(total_tiles);
+                    const unsigned c1 = (static_cast<unsigned>(C) * b1 + half) / static_cast<unsigned>(total_tiles);
+                    if (b1 > b0 && c1 <= c0) ok = false;
+                }
+            }
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        aligned = ok && al_pair >= 0;
+        if (aligned) {
+            const unsigned tiles_p = t1 - t0;
+            const unsigned n_p = static_cast<unsigned>(s1 - s0);
+            const unsigned n_eff = n_p < tiles_p ? n_p : tiles_p;  // never more CTAs than tiles
+            const unsigned k = static_cast<unsigned>(c - s0);
+            al_first = s0;
+            al_nseg = static_cast<int>(n_eff);
+            al_start = static_cast<int>(t0);
+            al_end = static_cast<int>(t1);
+            if (k < n_eff) {
+                if (tiles_p < (1u << 20)) {  // products fit 32 bits (n_eff <= C <= 4096)
+                    lo = static_cast<int>(t0 + tiles_p * k / n_eff);
+                    hi = static_cast<int>(t0 + tiles_p * (k + 1) / n_eff);
+                } else {
+                    lo = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * k / n_eff));
+                    hi = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * (k + 1) / n_eff));
+                }
+            }
+        }
+    }
+    if (!aligned) {
+        lo = range_lo(c);
+        hi = range_lo(c + 1);
+    }
+    SA_PSTAMP(3);
     // This warp's tiles are lo + warp + j*WARPS for j in [0, n_w), across all segments of the CTA,
     // so its copy pipeline keeps running through segment boundaries.
     const int n_w = hi - lo > warp ? (hi - lo - warp + WARPS - 1) / WARPS : 0;
 
     // What this lane has to copy for the warp's j-th tile (page-table lookups happen here, one
-    // tile before the copies are issued, so their latency stays off the critical path).
+    // tile before the copies are issued, so their latency stays off the critical path).  The
+    // producer keeps its own (row, kv head) cursor: tiles are visited in ascending order, so
+    // the cursor only moves when a tile crosses into the next pair.
+    int pc_b = -1, pc_kvh = 0, pc_start = 0, pc_end = 0;
+    int64_t pc_vlen = 0;
+    if (aligned && hi > lo) {  // all of this CTA's tiles belong to one pair: no search needed
+        pc_b = al_pair / Hkv;
+        pc_kvh = al_pair - pc_b * Hkv;
+        pc_start = al_start;
+        pc_end = al_end;
+        pc_vlen = row_vlen(p.seq, pc_b);
+    }
     auto lookup = [&](int j) -> Frag {
         Frag f;
         f.state = 0; f.tok = 0; f.outer = 0; f.kvh = 0; f.trace_idx = -1;
-        if (j >= n_w || lane >= p.frags_per_tile) return f;
-        int b, kvh, row_tiles, pair_start;
+        if (j >= n_w) return f;
         const int x = lo + warp + j * WARPS;
-        locate(x, b, kvh, row_tiles, pair_start);
-        f.kvh = kvh;
-        const unsigned vfrag = static_cast<unsigned>(x - pair_start) * p.frags_per_tile + lane;
-        const int64_t vtok0 = static_cast<int64_t>(vfrag) * p.frag_tokens;
-        if (vtok0 >= row_vlen(p.seq, b)) return f;
+        if (x >= pc_end) {
+            int b, row_tiles;
+            locate(x, b, pc_kvh, row_tiles, pc_start);
+            pc_end = pc_start + row_tiles;
+            if (b != pc_b) pc_vlen = row_vlen(p.seq, b);
+            pc_b = b;
+        }
+        f.kvh = pc_kvh;
+        if (lane >= p.frags_per_tile) return f;
+        const unsigned vfrag = (static_cast<unsigned>(x - pc_start) << p.fpt_shift) + lane;
+        const int64_t vtok0 = static_cast<int64_t>(vfrag) << p.frag_shift;
+        if (vtok0 >= pc_vlen) return f;
         if (p.seq.mode == kContig) {
             f.tok = static_cast<int>(vtok0);
-            f.outer = b;
+            f.outer = pc_b;
             f.state = 1;
         } else if (p.seq.mode == kPaged) {
-            const unsigned lp = vfrag / static_cast<unsigned>(p.frags_per_unit);
-            const int sub = static_cast<int>(vfrag - lp * p.frags_per_unit);
-            const int64_t slot = static_cast<int64_t>(b) * p.seq.max_pages + lp;
+            const unsigned lp = vfrag >> p.fpu_shift;
+            const int sub = static_cast<int>(vfrag - (lp << p.fpu_shift));
+            const int64_t slot = static_cast<int64_t>(pc_b) * p.seq.max_pages + lp;
             const int64_t page = load_index(p.seq.page_table, p.seq.table_i64, slot);
-            f.tok = sub * p.frag_tokens;
+            f.tok = sub << p.frag_shift;
             f.outer = static_cast<int>(page);
             f.state = (page >= 0 && page < p.seq.num_pages) ? 1 : 2;
-            if (kvh == 0 && sub == 0) f.trace_idx = slot;
+            if (pc_kvh == 0 && sub == 0) f.trace_idx = slot;
         } else {
-            const unsigned bi = vfrag / static_cast<unsigned>(p.frags_per_unit);
-            const int sub = static_cast<int>(vfrag - bi * p.frags_per_unit);
-            f.tok = p.seq.blocks[bi] * p.seq.block_size + sub * p.frag_tokens;
-            f.outer = b;
+            const unsigned bi = vfrag >> p.fpu_shift;
+            const int sub = static_cast<int>(vfrag - (bi << p.fpu_shift));
+            f.tok = p.seq.blocks[bi] * p.seq.block_size + (sub << p.frag_shift);
+            f.outer = pc_b;
             f.state = 1;
         }
         return f;
@@ -349,10 +473,14 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     };
 
     // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
+    Frag first[STAGES + 1];
+#pragma unroll
+    for (int s = 0; s <= STAGES; ++s) first[s] = lookup(s);  // all table loads in flight together
+    SA_PSTAMP(4);
 #pragma unroll
     for (int s = 0; s < STAGES; ++s)
-        if (s < n_w) issue(s, lookup(s));
-    Frag pending = lookup(STAGES);
+        if (s < n_w) issue(s, first[s]);
+    Frag pending = first[STAGES];
     SA_STAMP(1);
 
     // Rows with no tokens are not part of the tile list: write their (empty) result here.
@@ -381,7 +509,14 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     while (cur < hi) {
         // The segment: tiles [cur, seg_end) of one (row, kv head) pair.
         int b, kvh, row_tiles, pair_start;
-        locate(cur, b, kvh, row_tiles, pair_start);
+        if (aligned) {
+            b = al_pair / Hkv;
+            kvh = al_pair - b * Hkv;
+            pair_start = al_start;
+            row_tiles = al_end - al_start;
+        } else {
+            locate(cur, b, kvh, row_tiles, pair_start);
+        }
         const int pair_end = pair_start + row_tiles;
         const int seg_end = hi < pair_end ? hi : pair_end;
         const int pair = b * Hkv + kvh;
@@ -429,7 +564,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
             dead = __any_sync(0xffffffffu, dead);
             if (dead) continue;
-            if (j == 0) SA_STAMP(2);
+            if (j == 0) SA_STAMP(7);
 
             const int64_t tile_tok0 = static_cast<int64_t>(lt) * TILE_N;
             const int n_valid = vlen - tile_tok0 < TILE_N ? static_cast<int>(vlen - tile_tok0) : TILE_N;
@@ -593,8 +728,8 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 
         // Combine the warps of this CTA, then either finish the pair or publish a state.
         // Work items are 4 consecutive columns of one head row.
-        const int first_cta = owner(pair_start);
-        const int nseg = owner(pair_end - 1) - first_cta + 1;
+        const int first_cta = aligned ? al_first : owner(pair_start);
+        const int nseg = aligned ? al_nseg : owner(pair_end - 1) - first_cta + 1;
         const int64_t slot_stride = static_cast<int64_t>(group) * PART_STRIDE;
         float *my_slot = p.partials + (static_cast<int64_t>(c) + pair) * slot_stride;
         const int64_t out_row0 = static_cast<int64_t>(b) * p.q_heads + static_cast<int64_t>(kvh) * group;
@@ -642,15 +777,22 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
 
         if (nseg > 1) {
-            __threadfence();
+            // Ticket with release/acquire semantics at GPU scope: together with the CTA barriers
+            // it orders every thread's state stores before the merging CTA's loads.
             __syncthreads();
-            if (tid == 0) s_last = atomicAdd(p.counters + pair, 1) == nseg - 1;
+            if (tid == 0) {
+                int old_count;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
+                             : "=r"(old_count)
+                             : "l"(p.counters + pair)
+                             : "memory");
+                s_last = old_count == nseg - 1;
+            }
             __syncthreads();
             SA_STAMP(5);
             if (s_last) {
                 // Last CTA to arrive on this pair: exact merge of its nseg split states.  All loads
                 // are issued before they are needed (the states sit in L2, ~1 us away).
-                __threadfence();
                 const float *first_slot = p.partials + (static_cast<int64_t>(first_cta) + pair) * slot_stride;
                 constexpr int CAP = WARPS * STATE_FLOATS / 2;
                 float *sm_m = states;        // the state areas are free again: reuse them for (m, l)
@@ -795,6 +937,10 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStrea
     sp.frag_tokens = geo.frag_tokens;
     sp.frags_per_tile = geo.frags_per_tile;
     sp.frags_per_unit = geo.frags_per_unit;
+    auto log2i = [](int x) { int s = 0; while ((1 << s) < x) ++s; return s; };
+    sp.frag_shift = log2i(geo.frag_tokens);
+    sp.fpt_shift = log2i(geo.frags_per_tile);
+    sp.fpu_shift = log2i(geo.frags_per_unit);
     sp.tok_dim = geo.tok_dim;
     sp.uniform_tiles = geo.uniform_tiles;
     sp.seq = p.seq;
