@@ -35,9 +35,15 @@ import torch
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-# Keep stdout to the one JSON line: NCCL prints a version banner there at INFO/VERSION level.
-if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-    os.environ["NCCL_DEBUG"] = "WARN"
+# Keep stdout to the one JSON line: libraries (NCCL's version banner, for one) write to fd 1.
+# Everything written to stdout before the result goes to stderr; emit() writes the real stdout.
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    sys.stdout.flush()
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
 METRIC = "kv_bytes_per_second"
 UNIT = "GB/s"
@@ -187,7 +193,7 @@ def build_seed_c4(device):
     return plan.run, q, out, info, plan
 
 
-def build_cp_c5(device, rank, world):
+def build_cp_c5(device, rank, world, exchange="auto"):
     from streamattn_b200.context_parallel import ContextParallelExactDecode, shard_bounds
 
     Hq, Hkv, D, N = 32, 8, 128, 1048576
@@ -204,11 +210,11 @@ def build_cp_c5(device, rank, world):
         k[:, :, a - lo:b - lo] = kc[:, :, a - c0:b - c0]
         v[:, :, a - lo:b - lo] = vc[:, :, a - c0:b - c0]
         del kc, vc
-    cp = ContextParallelExactDecode(q, k, v, kv_layout="BHND")
+    cp = ContextParallelExactDecode(q, k, v, kv_layout="BHND", exchange=exchange)
     info = dict(workload="cp_c5", batch=1, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, shard_tokens=hi - lo,
                 kernel=cp.kernel_name, ctas=cp._plan.num_ctas, bytes=2 * Hkv * N * D * 2,
-                exchange_bytes_per_rank=cp.exchange_bytes_per_rank,
-                launches=2 if world == 1 else 3, parallelism=f"cp{world}")
+                exchange_bytes_per_rank=cp.exchange_bytes_per_rank, exchange=cp.exchange,
+                launches=cp.launches_per_run, parallelism=f"cp{world}")
     return cp.run, q, cp.output, info, cp
 
 
@@ -279,6 +285,8 @@ def main() -> None:
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "cp_c5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="cp_c5 only: how the per-rank states meet (fused peer-store kernel or NCCL all-gather)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + the timed region (for runs under ncu): no e2e, CPU or clock legs")
     args = ap.parse_args()
@@ -303,7 +311,7 @@ def main() -> None:
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
-        print(json.dumps(line))
+        emit(line)
         return
 
     if not torch.cuda.is_available():
@@ -332,7 +340,7 @@ def main() -> None:
     elif workload == "seed_c4":
         run, q_dev, out_dev, info, plan = build_seed_c4(device)
     else:
-        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world)
+        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world, args.exchange)
     alg_bytes = info.pop("bytes")
     launches = info.pop("launches")
 
@@ -370,7 +378,7 @@ def main() -> None:
 
     if args.profile:
         if rank == 0:
-            print(json.dumps({"profile_run": True, "workload": workload, "us_per_call": step_s * 1e6}))
+            emit({"profile_run": True, "workload": workload, "us_per_call": step_s * 1e6})
         if distributed:
             import torch.distributed as dist
 
@@ -436,7 +444,7 @@ def main() -> None:
             line["cp_speedup_vs_1gpu"] = single_gpu_us / (step_s * 1e6)
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_sample(workload)
-        print(json.dumps(line))
+        emit(line)
     if distributed:
         import torch.distributed as dist
 

@@ -216,6 +216,26 @@ SA_API int sa_merge_states(const float *states, int num_parts, int64_t rows, int
                            void *out, int out_dtype, sa_stream_t stream);
 
 /*
+ * Context-parallel exchange fused with the merge (no counterpart in the reference, which has no
+ * multi-GPU decode; the merge arithmetic is that of core/ring_attention.py:254-274).
+ * Every rank owns one exchange buffer of sa_cp_exchange_bytes() bytes, zero-filled once, that
+ * all ranks can address (peer-mapped / symmetric memory); peer_buffers is a HOST array with the
+ * address of every rank's buffer as seen from this GPU (index = rank).  One call per decode step
+ * on every rank, with the same step number (1, 2, 3, ...): the kernel stores local_state
+ * [rows, D+2] into every rank's buffer with plain peer stores, raises this rank's flag there,
+ * waits (at most 2 s, then SA_DEV_PIPELINE_TIMEOUT in the buffer's status word) for all ranks'
+ * flags and writes the merged out [rows, D].  Buffers are double-buffered by step parity.
+ */
+#define SA_CP_MAX_WORLD 16
+SA_API size_t sa_cp_exchange_bytes(int world_size, int64_t rows, int head_dim);
+SA_API int sa_cp_exchange_merge(const float *local_state, const uint64_t *peer_buffers, int world_size, int rank,
+                                uint32_t step, int64_t rows, int head_dim, void *out, int out_dtype,
+                                sa_stream_t stream);
+/* Synchronise and return (then clear) the status bits of an exchange buffer. */
+SA_API int sa_cp_exchange_status(void *exchange_buffer, int world_size, int64_t rows, int head_dim,
+                                 sa_stream_t stream);
+
+/*
  * Bound plans: validate once, keep the prepared launch (tensor maps, geometry),
  * run many times with no per-call setup - what ExactDecodePlan.run /
  * PagedExactDecodePlan.run do in the reference

@@ -7,8 +7,11 @@ KV sequence can be split across the GPUs of one box:
 * rank r owns tokens ``[r*N/G, (r+1)*N/G)`` of every (row, KV head);
 * each rank runs the exact kernel on its shard and emits the split state
   ``[B, Hq, D+2]`` (float32) instead of a normalised output;
-* one all-gather (NCCL over NVLink) brings the G states into each rank's own
-  memory and a local merge kernel produces the final output on every rank.
+* the G states are brought into each rank's own memory and merged exactly, on
+  every rank.  Two exchanges are provided: ``"peer"`` - one kernel that stores
+  the state into every rank's symmetric-memory buffer with plain peer stores
+  over NVLink, raises a flag, waits (bounded) for all ranks' flags and merges;
+  and ``"nccl"`` - ``all_gather_into_tensor`` followed by the merge kernel.
 
 The exchange is ``B*Hq*(D+2)*4`` bytes per rank (16.6 KB for one row of 32
 heads of 128), so it is latency- not bandwidth-bound.  Batch-parallel shapes
@@ -54,22 +57,44 @@ def gather_states(local_state: torch.Tensor, gathered: Optional[torch.Tensor] = 
     return gathered
 
 
+def _peer_exchange_buffers(nbytes: int, device: torch.device, group: Optional[dist.ProcessGroup]):
+    """Allocate this rank's exchange buffer in symmetric memory; returns (buffer, peer addresses)."""
+
+    if dist.get_world_size(group) == 1:
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        return buf, [int(buf.data_ptr())]
+    import torch.distributed._symmetric_memory as symm_mem
+
+    buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+    handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+    buf.zero_()
+    torch.cuda.synchronize(device)
+    dist.barrier(group)  # nobody may store into a buffer that is not yet cleared
+    ptrs = [int(x) for x in handle.buffer_ptrs]
+    return (buf, handle), ptrs
+
+
 class ContextParallelExactDecode:
     """Exact decode over a KV sequence sharded across the ranks of a process group.
 
-    Bound once to this rank's shard; ``run()`` launches the local kernel, the
-    all-gather and the merge on the current stream and allocates nothing.
+    Bound once to this rank's shard; ``run()`` launches the local kernel and the
+    exchange + merge on the current stream and allocates nothing.
     ``key_shard`` / ``value_shard`` hold this rank's tokens only, in ``kv_layout``
     (``"BHND"`` head-major by default).  ``shard_lens`` optionally gives per-row
-    valid token counts inside the shard (ragged rows).
+    valid token counts inside the shard (ragged rows).  ``exchange`` selects how
+    the per-rank states meet: ``"peer"`` (fused peer-store kernel over symmetric
+    memory), ``"nccl"`` (all-gather then merge) or ``"auto"`` (peer when symmetric
+    memory can be set up, otherwise nccl; every rank takes the same decision).
     """
 
     def __init__(self, query: torch.Tensor, key_shard: torch.Tensor, value_shard: torch.Tensor, *,
                  kv_layout: str = "BHND", group: Optional[dist.ProcessGroup] = None,
                  output: Optional[torch.Tensor] = None, shard_lens: Optional[torch.Tensor] = None,
-                 num_ctas: int = 0, kernel: str = "auto") -> None:
+                 num_ctas: int = 0, kernel: str = "auto", exchange: str = "auto") -> None:
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised for context-parallel decode")
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("exchange must be auto, peer or nccl")
         native.require_cuda(query, key_shard, value_shard)
         self.group = group
         self.world_size = dist.get_world_size(group)
@@ -79,14 +104,37 @@ class ContextParallelExactDecode:
         kv_heads = int(key_shard.shape[1] if kv_layout == "BHND" else key_shard.shape[2])
         self.output = torch.empty_like(query) if output is None else output
         self.local_state = torch.empty(batch, q_heads, dim + 2, dtype=torch.float32, device=query.device)
-        self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
-                                    device=query.device)
         self.workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
         self._plan = native.exact_plan(query, key_shard, value_shard, self.local_state, self.workspace,
                                        kv_layout=kv_layout, seq_lens=shard_lens, out_state=True,
                                        num_ctas=num_ctas, kernel=kernel)
         self._rows = batch * q_heads
         self._dim = dim
+        self._peer: Optional[native.PeerExchange] = None
+        self._peer_keepalive = None
+        self.exchange_fallback_reason: Optional[str] = None
+        if exchange in ("auto", "peer") and self.world_size <= 16:
+            ok, reason = True, None
+            try:
+                nbytes = native.cp_exchange_bytes(self.world_size, self._rows, dim)
+                keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
+                self._peer = native.PeerExchange(self.local_state, ptrs, self.rank, self.output)
+                self._peer_keepalive = keep
+            except Exception as exc:  # symmetric memory unavailable on this system
+                if exchange == "peer":
+                    raise
+                ok, reason = False, f"{type(exc).__name__}: {exc}"
+            if exchange == "auto" and self.world_size > 1:
+                # All ranks must use the same exchange: fall back together if any rank failed.
+                flag = torch.tensor([1 if ok else 0], device=query.device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+                if int(flag.item()) == 0:
+                    self._peer, self._peer_keepalive = None, None
+                    self.exchange_fallback_reason = reason or "another rank could not set up symmetric memory"
+        self.exchange = "peer" if self._peer is not None else "nccl"
+        if self._peer is None:
+            self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
+                                        device=query.device)
 
     @property
     def kernel_name(self) -> str:
@@ -96,10 +144,19 @@ class ContextParallelExactDecode:
     def exchange_bytes_per_rank(self) -> int:
         return self.local_state.numel() * 4
 
-    def device_status(self) -> int:
-        """Synchronise and return the local kernel's status bits (0 = clean)."""
+    @property
+    def launches_per_run(self) -> int:
+        """Kernels of this package per run (the NCCL collective is not counted)."""
 
-        return native.workspace_status(self.workspace)
+        return self._plan.launches + 1
+
+    def device_status(self) -> int:
+        """Synchronise and return the status bits of the local kernel and the exchange (0 = clean)."""
+
+        status = native.workspace_status(self.workspace)
+        if self._peer is not None:
+            status |= self._peer.status()
+        return status
 
     def run_local(self) -> torch.Tensor:
         """Only the local shard kernel; returns this rank's state."""
@@ -109,6 +166,9 @@ class ContextParallelExactDecode:
 
     def run(self) -> torch.Tensor:
         self._plan.run()
+        if self._peer is not None:
+            self._peer.run()
+            return self.output
         if self.world_size == 1:
             states = self.local_state.view(1, self._rows, self._dim + 2)
         else:

@@ -567,6 +567,42 @@ int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_d
     return SA_OK;
 }
 
+size_t sa_cp_exchange_bytes(int world_size, int64_t rows, int head_dim)
+{
+    if (world_size <= 0 || world_size > SA_CP_MAX_WORLD || rows <= 0 || head_dim <= 0) {
+        fail(SA_ERR_INVALID, "sa_cp_exchange_bytes: bad argument");
+        return 0;
+    }
+    return exchange_bytes(world_size, rows, head_dim);
+}
+
+int sa_cp_exchange_merge(const float *local_state, const uint64_t *peer_buffers, int world_size, int rank,
+                         uint32_t step, int64_t rows, int head_dim, void *out, int out_dtype, sa_stream_t stream)
+{
+    if (!local_state || !peer_buffers || !out || rows <= 0 || head_dim <= 0)
+        return fail(SA_ERR_INVALID, "sa_cp_exchange_merge: bad argument");
+    if (world_size <= 0 || world_size > SA_CP_MAX_WORLD || rank < 0 || rank >= world_size)
+        return fail(SA_ERR_INVALID, "sa_cp_exchange_merge: world_size must be in [1, %d] and rank inside it",
+                    SA_CP_MAX_WORLD);
+    if (step == 0) return fail(SA_ERR_INVALID, "sa_cp_exchange_merge: step counts from 1");
+    if (out_dtype < SA_DTYPE_BF16 || out_dtype > SA_DTYPE_F32) return fail(SA_ERR_INVALID, "unknown out_dtype");
+    for (int i = 0; i < world_size; ++i)
+        if (peer_buffers[i] == 0 || peer_buffers[i] % 128)
+            return fail(SA_ERR_INVALID, "sa_cp_exchange_merge: peer buffer %d is null or not 128-byte aligned", i);
+    cudaError_t err = launch_exchange_merge(local_state, peer_buffers, world_size, rank, step, rows, head_dim, out,
+                                            out_dtype, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_cp_exchange_merge");
+    return SA_OK;
+}
+
+int sa_cp_exchange_status(void *exchange_buffer, int world_size, int64_t rows, int head_dim, sa_stream_t stream)
+{
+    if (!exchange_buffer || world_size <= 0 || world_size > SA_CP_MAX_WORLD || rows <= 0 || head_dim <= 0)
+        return -SA_ERR_INVALID;
+    return sa_workspace_status(static_cast<char *>(exchange_buffer) + exchange_status_offset(world_size, rows, head_dim),
+                               stream);
+}
+
 // ---------------------------------------------------------------------------
 // Exact decode without any allocation: the scratch lives in this module's image.
 // ---------------------------------------------------------------------------

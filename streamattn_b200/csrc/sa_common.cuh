@@ -130,6 +130,12 @@ size_t generic_partial_floats(int batch, int q_heads, int head_dim, int splits);
 cudaError_t launch_merge_states(const float *states, int parts, int64_t rows, int dim, void *out,
                                 int out_dtype, cudaStream_t stream);
 
+size_t exchange_bytes(int world, int64_t rows, int dim);
+size_t exchange_status_offset(int world, int64_t rows, int dim);
+cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *bases_host, int world, int rank,
+                                  uint32_t step, int64_t rows, int dim, void *out, int out_dtype,
+                                  cudaStream_t stream);
+
 struct StreamGeometry;  // defined in sa_stream.cuh
 
 }  // namespace sa

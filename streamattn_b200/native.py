@@ -65,6 +65,9 @@ _SIGNATURES = {
     "sa_seed_decode": (_SEED_COMMON + [_i, _i, _i, _i, _i, _i, _i, _vp], _i),
     "sa_seed_decode_blocks": (_SEED_COMMON + [_i, _i32p, _i, _i, _i, _vp], _i),
     "sa_merge_states": ([_vp, _i, _i64, _i, _vp, _i, _vp], _i),
+    "sa_cp_exchange_bytes": ([_i, _i64, _i], _sz),
+    "sa_cp_exchange_merge": ([_vp, ctypes.POINTER(ctypes.c_uint64), _i, _i, ctypes.c_uint32, _i64, _i, _vp, _i, _vp], _i),
+    "sa_cp_exchange_status": ([_vp, _i, _i64, _i, _vp], _i),
     "sa_exact_plan_create": (_EXACT_ARGS, _vp),
     "sa_paged_plan_create": (_PAGED_ARGS, _vp),
     "sa_seed_plan_create": (_SEED_COMMON + [_i, _i32p, _i, _i, _i], _vp),
@@ -408,3 +411,48 @@ def merge_states(states: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
                                     SA_DTYPE[output.dtype], stream_handle(device))
     check(rc)
     return output
+
+
+def cp_exchange_bytes(world_size: int, rows: int, head_dim: int) -> int:
+    n = int(load().sa_cp_exchange_bytes(world_size, rows, head_dim))
+    if n == 0:
+        raise ValueError(last_error())
+    return n
+
+
+class PeerExchange:
+    """Bound ``sa_cp_exchange_merge`` call: peer addresses fixed, step counter kept here."""
+
+    def __init__(self, local_state: torch.Tensor, peer_buffer_ptrs: Sequence[int], rank: int,
+                 output: torch.Tensor) -> None:
+        device = require_cuda(local_state, output)
+        if local_state.dtype != torch.float32 or local_state.dim() != 3 or not local_state.is_contiguous():
+            raise ValueError("local_state must be a contiguous float32 [batch, heads, dim + 2] tensor")
+        self.world = len(peer_buffer_ptrs)
+        self.rank = int(rank)
+        self.rows = int(local_state.shape[0] * local_state.shape[1])
+        self.dim = int(local_state.shape[2]) - 2
+        if output.numel() != self.rows * self.dim or not output.is_contiguous() or output.dtype not in SA_DTYPE:
+            raise ValueError("output must be contiguous with rows * dim elements")
+        self._ptrs = (ctypes.c_uint64 * self.world)(*[int(x) for x in peer_buffer_ptrs])
+        self._local_buffer = int(peer_buffer_ptrs[self.rank])
+        self._state = local_state
+        self._out = output
+        self._device_index = device.index if device.index is not None else torch.cuda.current_device()
+        self._fn = load().sa_cp_exchange_merge
+        self._dtype = SA_DTYPE[output.dtype]
+        self.step = 0
+
+    def run(self) -> None:
+        self.step += 1
+        rc = self._fn(self._state.data_ptr(), self._ptrs, self.world, self.rank, self.step, self.rows, self.dim,
+                      self._out.data_ptr(), self._dtype, _current_raw_stream(self._device_index))
+        if rc:
+            check(rc)
+
+    def status(self) -> int:
+        rc = int(load().sa_cp_exchange_status(self._local_buffer, self.world, self.rows, self.dim,
+                                              _current_raw_stream(self._device_index)))
+        if rc < 0:
+            raise RuntimeError(last_error())
+        return rc
