@@ -53,7 +53,9 @@ class ExactDecodePlan:
               seq_lens: Optional[torch.Tensor] = None, kernel: str = "auto") -> "ExactDecodePlan":
         """Bind a plan.
 
-        ``kv_layout`` is ``"BHND"`` (head-major ``[B, Hkv, N, D]``, what the
+        ``query`` and ``output`` may be pinned host tensors (the kernel then reads
+        the query and writes the result across PCIe itself, saving the two copies a
+        host-driven decode step would otherwise enqueue).  ``kv_layout`` is ``"BHND"`` (head-major ``[B, Hkv, N, D]``, what the
         reference's plan takes) or ``"BNHD"``; by default head-major is assumed,
         as in the reference.  ``num_splits`` asks for that many CTAs per
         (row, KV head); ``None`` sizes the grid to the GPU.  ``promoted_only``
@@ -62,7 +64,7 @@ class ExactDecodePlan:
         """
 
         del promoted_only
-        native.require_cuda(query, key_cache, value_cache)
+        native.require_cuda(key_cache, value_cache, host_io=(query, output))
         layout = kv_layout or "BHND"
         if query.dim() != 4 or key_cache.dim() != 4 or value_cache.dim() != 4:
             raise ValueError("unsupported exact decode buffers: rank")
@@ -71,15 +73,15 @@ class ExactDecodePlan:
         if kv_heads <= 0 or q_heads % kv_heads:
             raise ValueError("unsupported exact decode buffers: gqa")
         if output is None:
-            output = torch.empty_like(query)
+            output = torch.empty(query.shape, dtype=query.dtype, device=key_cache.device)
         if output.shape != query.shape or output.dtype != query.dtype:
             raise ValueError("output must match query shape and dtype")
-        if not output.is_cuda or not output.is_contiguous():
-            raise ValueError("output must be a contiguous CUDA tensor")
+        if not (output.is_cuda or output.is_pinned()) or not output.is_contiguous():
+            raise ValueError("output must be a contiguous CUDA (or pinned host) tensor")
         if num_splits is not None and num_splits <= 0:
             raise ValueError("num_splits must be positive")
         num_ctas = 0 if num_splits is None else int(num_splits) * batch * kv_heads
-        workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
+        workspace = native.new_workspace(key_cache.device, batch, q_heads, kv_heads, dim, num_ctas)
         plan = native.exact_plan(query, key_cache, value_cache, output, workspace, kv_layout=layout,
                                  seq_lens=seq_lens, num_ctas=num_ctas, kernel=kernel)
         pairs = batch * kv_heads

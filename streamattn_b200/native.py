@@ -133,10 +133,21 @@ def check(rc: int) -> None:
     raise RuntimeError(msg or f"streamattn_b200 native error {rc}")
 
 
-def require_cuda(*tensors: torch.Tensor) -> torch.device:
-    """All tensors must live on one CUDA device; there is no CPU execution path."""
+def require_cuda(*tensors: torch.Tensor, host_io: Sequence[torch.Tensor] = ()) -> torch.device:
+    """All tensors must live on one CUDA device; there is no CPU execution path.
+
+    Tensors listed in ``host_io`` (the query and the output of a plan) may instead be pinned
+    host tensors: pinned memory is addressable from the GPU, so the kernels read the query and
+    write the result across PCIe themselves and no separate copy is enqueued.
+    """
 
     devices = {t.device for t in tensors if t is not None}
+    for t in host_io:
+        if t is None:
+            continue
+        if t.device.type == "cpu" and t.is_pinned():
+            continue
+        devices.add(t.device)
     if len(devices) != 1:
         raise ValueError("all tensors of a decode call must share one device")
     device = next(iter(devices))
@@ -274,7 +285,7 @@ def exact_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, outp
                workspace: torch.Tensor, *, kv_layout: str = "BNHD",
                seq_lens: Optional[torch.Tensor] = None, out_state: bool = False,
                num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
-    device = require_cuda(query, key, value, output, workspace, seq_lens)
+    device = require_cuda(key, value, workspace, seq_lens, host_io=(query, output))
     if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
         raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
     q_sb, q_sh = _q_strides(query)
@@ -342,7 +353,7 @@ def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.
                page_table: torch.Tensor, seq_lens: torch.Tensor, output: torch.Tensor,
                workspace: torch.Tensor, *, layout: str, trace: Optional[torch.Tensor] = None,
                out_state: bool = False, num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
-    device = require_cuda(query, key_pages, value_pages, page_table, seq_lens, output, workspace, trace)
+    device = require_cuda(key_pages, value_pages, page_table, seq_lens, workspace, trace, host_io=(query, output))
     layout = layout.upper()
     if layout not in SA_LAYOUT:
         raise ValueError("paged KV layout must be NHD or HND")
