@@ -285,7 +285,7 @@ def main() -> None:
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "cp_c5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "peer", "nccl"],
                     help="cp_c5 only: how the per-rank states meet (fused peer-store kernel or NCCL all-gather)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + the timed region (for runs under ncu): no e2e, CPU or clock legs")
@@ -427,6 +427,15 @@ def main() -> None:
     per_gpu_bytes = alg_bytes / world if workload == "cp_c5" else alg_bytes
     achieved = per_gpu_bytes / step_s / 1e9
 
+    local_kernel_us = None
+    if workload == "cp_c5":
+        # The shard kernel alone (no exchange): what the exchange + rank skew add is the difference.
+        for _ in range(3):
+            plan.run_local()
+        barrier()
+        local_kernel_us = max_over_ranks(time_region(plan.run_local, 100, device)) / 100 * 1e6
+        barrier()
+
     single_gpu_us = None
     if workload == "cp_c5" and world > 1 and rank == 0:
         # One-GPU time of the same 1M-token row, measured in this run on rank 0 (not in the timed region).
@@ -457,6 +466,8 @@ def main() -> None:
             "clocks": clocks.summary(),
             "device_status": status,
         }
+        if local_kernel_us is not None:
+            line["cp_local_kernel_us"] = local_kernel_us
         if single_gpu_us is not None:
             line["cp_single_gpu_us"] = single_gpu_us
             line["cp_speedup_vs_1gpu"] = single_gpu_us / (step_s * 1e6)

@@ -34,6 +34,7 @@ extern "C" {
 #endif
 
 typedef void *sa_stream_t; /* cudaStream_t */
+typedef struct sa_plan sa_plan_t; /* bound plan, see the end of this header */
 
 enum sa_status {
     SA_OK = 0,
@@ -236,6 +237,27 @@ SA_API int sa_cp_exchange_status(void *exchange_buffer, int world_size, int64_t 
                                  sa_stream_t stream);
 
 /*
+ * Context-parallel decode in ONE launch per step (no counterpart in the reference): the shard's
+ * exact decode, the state exchange and the cross-rank merge fused.  The CTA that completes a
+ * (row, KV head) pair on this rank stores the pair's state rows into every rank's exchange buffer
+ * (plain peer stores), raises the pair's flag there, waits (at most 2 s, then
+ * SA_DEV_PIPELINE_TIMEOUT in the workspace status word) for the same pair from all ranks and writes
+ * the merged rows of out [batch, q_heads, D].  Up to 8 ranks; bf16/fp16, head_dim 64/128 (the
+ * streaming kernel); uniform shard length.  Each rank's exchange buffer has
+ * sa_cp_fused_bytes() bytes, is zero-filled once and addressable by all ranks; peer_buffers is a
+ * HOST array of its address on every rank (index = rank).  Every sa_plan_run() of the returned
+ * plan is one step; all ranks must run their plans the same number of times.
+ */
+SA_API size_t sa_cp_fused_bytes(int world_size, int batch, int q_heads, int kv_heads, int head_dim);
+SA_API sa_plan_t *sa_cp_fused_plan_create(const void *q, const void *k, const void *v, void *out,
+                                          void *workspace, size_t workspace_bytes,
+                                          int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                          int64_t q_stride_b, int64_t q_stride_h,
+                                          int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                          int dtype, int num_ctas,
+                                          const uint64_t *peer_buffers, int world_size, int rank);
+
+/*
  * Bound plans: validate once, keep the prepared launch (tensor maps, geometry),
  * run many times with no per-call setup - what ExactDecodePlan.run /
  * PagedExactDecodePlan.run do in the reference
@@ -243,8 +265,6 @@ SA_API int sa_cp_exchange_status(void *exchange_buffer, int world_size, int64_t 
  * the same arguments as the one-shot calls (without the stream) and return NULL
  * on error.  A plan holds pointers, not ownership; the buffers must outlive it.
  */
-typedef struct sa_plan sa_plan_t;
-
 SA_API sa_plan_t *sa_exact_plan_create(const void *q, const void *k, const void *v, void *out,
                                        void *workspace, size_t workspace_bytes,
                                        const void *seq_lens, int lens_dtype,

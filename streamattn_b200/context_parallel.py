@@ -8,7 +8,9 @@ KV sequence can be split across the GPUs of one box:
 * each rank runs the exact kernel on its shard and emits the split state
   ``[B, Hq, D+2]`` (float32) instead of a normalised output;
 * the G states are brought into each rank's own memory and merged exactly, on
-  every rank.  Two exchanges are provided: ``"peer"`` - one kernel that stores
+  every rank.  Three exchanges are provided: ``"fused"`` - the whole step is ONE launch: the
+  CTA that completes a (row, KV head) pair stores its state rows to every rank, raises the
+  pair's flag, waits (bounded) for the other ranks' flags and merges; ``"peer"`` - one extra kernel that stores
   the state into every rank's symmetric-memory buffer with plain peer stores
   over NVLink, raises a flag, waits (bounded) for all ranks' flags and merges;
   and ``"nccl"`` - ``all_gather_into_tensor`` followed by the merge kernel.
@@ -82,9 +84,10 @@ class ContextParallelExactDecode:
     ``key_shard`` / ``value_shard`` hold this rank's tokens only, in ``kv_layout``
     (``"BHND"`` head-major by default).  ``shard_lens`` optionally gives per-row
     valid token counts inside the shard (ragged rows).  ``exchange`` selects how
-    the per-rank states meet: ``"peer"`` (fused peer-store kernel over symmetric
-    memory), ``"nccl"`` (all-gather then merge) or ``"auto"`` (peer when symmetric
-    memory can be set up, otherwise nccl; every rank takes the same decision).
+    the per-rank states meet: ``"fused"`` (decode + exchange + merge in one launch, up
+    to 8 ranks), ``"peer"`` (a separate peer-store exchange + merge kernel), ``"nccl"``
+    (all-gather then merge) or ``"auto"`` (the first of these that can be set up on
+    every rank; all ranks take the same decision).
     """
 
     def __init__(self, query: torch.Tensor, key_shard: torch.Tensor, value_shard: torch.Tensor, *,
@@ -93,8 +96,8 @@ class ContextParallelExactDecode:
                  num_ctas: int = 0, kernel: str = "auto", exchange: str = "auto") -> None:
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised for context-parallel decode")
-        if exchange not in ("auto", "peer", "nccl"):
-            raise ValueError("exchange must be auto, peer or nccl")
+        if exchange not in ("auto", "fused", "peer", "nccl"):
+            raise ValueError("exchange must be auto, fused, peer or nccl")
         native.require_cuda(query, key_shard, value_shard)
         self.group = group
         self.world_size = dist.get_world_size(group)
@@ -111,28 +114,54 @@ class ContextParallelExactDecode:
         self._rows = batch * q_heads
         self._dim = dim
         self._peer: Optional[native.PeerExchange] = None
-        self._peer_keepalive = None
+        self._fused: Optional[native.NativePlan] = None
+        self._keepalive = None
         self.exchange_fallback_reason: Optional[str] = None
-        if exchange in ("auto", "peer") and self.world_size <= 16:
-            ok, reason = True, None
+
+        def agree(ok: bool) -> bool:
+            """All ranks must use the same exchange: a mode is taken only if it works everywhere."""
+
+            if self.world_size == 1:
+                return ok
+            flag = torch.tensor([1 if ok else 0], device=query.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            return bool(int(flag.item()))
+
+        def attempt(mode: str, build) -> bool:
+            ok = True
             try:
-                nbytes = native.cp_exchange_bytes(self.world_size, self._rows, dim)
-                keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
-                self._peer = native.PeerExchange(self.local_state, ptrs, self.rank, self.output)
-                self._peer_keepalive = keep
-            except Exception as exc:  # symmetric memory unavailable on this system
-                if exchange == "peer":
+                build()
+            except Exception as exc:  # symmetric memory unavailable, shape not covered, ...
+                if exchange == mode:
                     raise
-                ok, reason = False, f"{type(exc).__name__}: {exc}"
-            if exchange == "auto" and self.world_size > 1:
-                # All ranks must use the same exchange: fall back together if any rank failed.
-                flag = torch.tensor([1 if ok else 0], device=query.device)
-                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-                if int(flag.item()) == 0:
-                    self._peer, self._peer_keepalive = None, None
-                    self.exchange_fallback_reason = reason or "another rank could not set up symmetric memory"
-        self.exchange = "peer" if self._peer is not None else "nccl"
-        if self._peer is None:
+                ok = False
+                self.exchange_fallback_reason = f"{mode}: {type(exc).__name__}: {exc}"
+            if not agree(ok):
+                self._fused = self._peer = self._keepalive = None
+                return False
+            return True
+
+        def build_fused() -> None:
+            if shard_lens is not None:
+                raise ValueError("the fused exchange needs a uniform shard length")
+            nbytes = native.cp_fused_bytes(self.world_size, batch, q_heads, kv_heads, dim)
+            keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
+            self._fused = native.cp_fused_plan(query, key_shard, value_shard, self.output, self.workspace, ptrs,
+                                               self.rank, kv_layout=kv_layout, num_ctas=num_ctas)
+            self._keepalive = keep
+
+        def build_peer() -> None:
+            nbytes = native.cp_exchange_bytes(self.world_size, self._rows, dim)
+            keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
+            self._peer = native.PeerExchange(self.local_state, ptrs, self.rank, self.output)
+            self._keepalive = keep
+
+        self.exchange = "nccl"
+        if exchange in ("auto", "fused") and self.world_size <= 8 and kernel != "generic" and attempt("fused", build_fused):
+            self.exchange = "fused"
+        elif exchange in ("auto", "peer") and self.world_size <= 16 and attempt("peer", build_peer):
+            self.exchange = "peer"
+        if self.exchange == "nccl":
             self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
                                         device=query.device)
 
@@ -148,7 +177,7 @@ class ContextParallelExactDecode:
     def launches_per_run(self) -> int:
         """Kernels of this package per run (the NCCL collective is not counted)."""
 
-        return self._plan.launches + 1
+        return 1 if self._fused is not None else self._plan.launches + 1
 
     def device_status(self) -> int:
         """Synchronise and return the status bits of the local kernel and the exchange (0 = clean)."""
@@ -165,6 +194,9 @@ class ContextParallelExactDecode:
         return self.local_state
 
     def run(self) -> torch.Tensor:
+        if self._fused is not None:
+            self._fused.run()
+            return self.output
         self._plan.run()
         if self._peer is not None:
             self._peer.run()

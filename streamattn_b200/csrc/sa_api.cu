@@ -126,6 +126,7 @@ bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
 struct sa_plan {
     sa::Problem problem;
     int device;  // device that was current when the plan was made
+    mutable sa::CpFuse cp;  // cp.world == 0 unless made by sa_cp_fused_plan_create; cp.step counts runs
     bool use_stream;
     sa::StreamGeometry geo;
     int generic_splits;
@@ -270,7 +271,8 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
 
 int run_plan(const sa_plan *plan, cudaStream_t stream)
 {
-    cudaError_t err = plan->use_stream ? launch_stream(plan->problem, plan->geo, stream)
+    if (plan->cp.world > 0) plan->cp.step += 1;  // every rank advances in lock step, one per run
+    cudaError_t err = plan->use_stream ? launch_stream(plan->problem, plan->geo, plan->cp, stream)
                                        : launch_generic(plan->problem, plan->generic_splits, stream);
     if (err != cudaSuccess) return fail_cuda(err, "kernel launch failed");
     return SA_OK;
@@ -565,6 +567,73 @@ int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_d
                                           static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess) return fail_cuda(err, "sa_merge_states");
     return SA_OK;
+}
+
+namespace {
+
+struct FusedLayout {
+    size_t gather_floats_per_parity, flags_offset, total_bytes;
+};
+
+FusedLayout fused_layout(int world, int batch, int q_heads, int kv_heads, int head_dim)
+{
+    FusedLayout l;
+    l.gather_floats_per_parity = static_cast<size_t>(world) * batch * q_heads * (head_dim + 2);
+    l.flags_offset = (2 * l.gather_floats_per_parity * 4 + 127) / 128 * 128;
+    l.total_bytes = l.flags_offset + 2ull * kCpMaxWorld * batch * kv_heads * 4;
+    return l;
+}
+
+}  // namespace
+
+size_t sa_cp_fused_bytes(int world_size, int batch, int q_heads, int kv_heads, int head_dim)
+{
+    if (world_size <= 0 || world_size > kCpFuseWorld || batch <= 0 || q_heads <= 0 || kv_heads <= 0 ||
+        head_dim <= 0) {
+        fail(SA_ERR_INVALID, "sa_cp_fused_bytes: bad argument (world_size must be in [1, %d])", kCpFuseWorld);
+        return 0;
+    }
+    return fused_layout(world_size, batch, q_heads, kv_heads, head_dim).total_bytes;
+}
+
+sa_plan_t *sa_cp_fused_plan_create(const void *q, const void *k, const void *v, void *out, void *workspace,
+                                   size_t workspace_bytes, int batch, int q_heads, int kv_heads, int head_dim,
+                                   int64_t kv_len, int64_t q_stride_b, int64_t q_stride_h, int64_t kv_stride_b,
+                                   int64_t kv_stride_n, int64_t kv_stride_h, int dtype, int num_ctas,
+                                   const uint64_t *peer_buffers, int world_size, int rank)
+{
+    if (!peer_buffers || world_size <= 0 || world_size > kCpFuseWorld || rank < 0 || rank >= world_size) {
+        fail(SA_ERR_INVALID, "sa_cp_fused_plan_create: world_size must be in [1, %d] and rank inside it", kCpFuseWorld);
+        return nullptr;
+    }
+    for (int i = 0; i < world_size; ++i)
+        if (peer_buffers[i] == 0 || peer_buffers[i] % 128) {
+            fail(SA_ERR_INVALID, "sa_cp_fused_plan_create: peer buffer %d is null or not 128-byte aligned", i);
+            return nullptr;
+        }
+    sa_plan *plan = new (std::nothrow) sa_plan;
+    if (!plan) return nullptr;
+    // The shard kernel runs in state mode; its state rows go to the ranks' buffers, not to `out`.
+    if (fill_exact(plan, q, k, v, out, workspace, workspace_bytes, nullptr, SA_INDEX_I32, batch, q_heads, kv_heads,
+                   head_dim, kv_len, q_stride_b, q_stride_h, kv_stride_b, kv_stride_n, kv_stride_h, dtype,
+                   SA_OUT_STATE, num_ctas, SA_KERNEL_STREAM)) {
+        delete plan;
+        return nullptr;
+    }
+    if (reinterpret_cast<uintptr_t>(out) % 16) {
+        fail(SA_ERR_INVALID, "sa_cp_fused_plan_create: output must be 16-byte aligned");
+        delete plan;
+        return nullptr;
+    }
+    const FusedLayout l = fused_layout(world_size, batch, q_heads, kv_heads, head_dim);
+    plan->cp.world = world_size;
+    plan->cp.rank = rank;
+    plan->cp.step = 0;
+    for (int i = 0; i < kCpMaxWorld; ++i) plan->cp.bases[i] = i < world_size ? peer_buffers[i] : 0;
+    plan->cp.gather_floats_per_parity = l.gather_floats_per_parity;
+    plan->cp.flags_offset = l.flags_offset;
+    plan->cp.final_out = out;
+    return plan;
 }
 
 size_t sa_cp_exchange_bytes(int world_size, int64_t rows, int head_dim)

@@ -113,29 +113,44 @@ exchange_merge_kernel(const __grid_constant__ ExchangeParams p)
     }
     __syncthreads();
 
-    // (4) exact merge of the world states of each row.
+    // (4) exact merge of the world states of each row.  The states were written by peers, so
+    // they are read from L2 (ld.cg); every load of a row is issued before the first one is
+    // needed - a chain of dependent L2 round trips per rank would cost more than the exchange.
+    __shared__ float s_m[kExchangeMaxWorld], s_l[kExchangeMaxWorld], s_w[kExchangeMaxWorld];
     const float *gather = reinterpret_cast<const float *>(my_base) + parity * p.gather_floats_per_parity;
+    const size_t rank_stride = static_cast<size_t>(p.rows) * width;
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-        float big = -INFINITY;
-        for (int r = 0; r < p.world; ++r) {
-            const float *st = gather + (static_cast<size_t>(r) * p.rows + row) * width;
-            if (__ldcg(st + p.dim + 1) > 0.0f) big = fmaxf(big, __ldcg(st + p.dim));
-        }
-        float total_l = 0.0f;
-        for (int r = 0; r < p.world; ++r) {
-            const float *st = gather + (static_cast<size_t>(r) * p.rows + row) * width;
-            const float l = __ldcg(st + p.dim + 1);
-            if (l > 0.0f) total_l += exp2_diff(__ldcg(st + p.dim), big) * l;
-        }
-        for (int d = tid; d < p.dim; d += kExchangeThreads) {
-            float acc = 0.0f;
-#pragma unroll 4
-            for (int r = 0; r < p.world; ++r) {
-                const float *st = gather + (static_cast<size_t>(r) * p.rows + row) * width;
-                if (__ldcg(st + p.dim + 1) > 0.0f) acc += exp2_diff(__ldcg(st + p.dim), big) * __ldcg(st + d);
+        const float *row0 = gather + row * width;
+        if (tid < kExchangeMaxWorld) {
+            float m = -INFINITY, l = 0.0f;
+            if (tid < p.world) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(row0 + tid * rank_stride + p.dim));
+                m = ml.x;
+                l = ml.y;
             }
-            static_cast<OutT *>(p.out)[row * p.dim + d] = Elem<OutT>::from_float(total_l > 0.0f ? acc / total_l : 0.0f);
+            s_m[tid] = l > 0.0f ? m : -INFINITY;
+            s_l[tid] = l;
         }
+        __syncthreads();
+        float big = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < kExchangeMaxWorld; ++r) big = fmaxf(big, s_m[r]);
+        if (tid < kExchangeMaxWorld) s_w[tid] = exp2_diff(s_m[tid], big);
+        __syncthreads();
+        float total_l = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kExchangeMaxWorld; ++r) total_l += s_w[r] * s_l[r];
+        const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
+        for (int d = tid; d < p.dim; d += kExchangeThreads) {
+            float o[kExchangeMaxWorld];
+#pragma unroll
+            for (int r = 0; r < kExchangeMaxWorld; ++r) o[r] = r < p.world ? __ldcg(row0 + r * rank_stride + d) : 0.0f;
+            float acc = 0.0f;
+#pragma unroll
+            for (int r = 0; r < kExchangeMaxWorld; ++r) acc += s_w[r] * o[r];
+            static_cast<OutT *>(p.out)[row * p.dim + d] = Elem<OutT>::from_float(acc * inv);
+        }
+        __syncthreads();  // s_m / s_l / s_w are reused by the next row
     }
 }
 

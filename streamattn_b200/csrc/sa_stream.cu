@@ -49,6 +49,7 @@ struct StreamParams {
     int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
     SeqDesc seq;
+    CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
     unsigned long long *timeline;  // debug builds only: 8 globaltimer stamps per CTA
 #endif
@@ -739,6 +740,17 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 T *dst = static_cast<T *>(p.out) + (out_row0 + row) * D + d4;
                 *reinterpret_cast<uint2 *>(dst) =
                     make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
+            } else if (p.cp.world > 0) {
+                // Context-parallel: this rank's state row goes straight into every rank's gather
+                // buffer (plain peer stores over NVLink, own copy included).
+                const size_t off = (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
+                                   (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0 + row) * STATE_STRIDE;
+                for (int r = 0; r < p.cp.world; ++r) {
+                    float *dst = reinterpret_cast<float *>(p.cp.bases[r]) + off;
+                    *reinterpret_cast<float2 *>(dst + d4) = make_float2(acc.x, acc.y);
+                    *reinterpret_cast<float2 *>(dst + d4 + 2) = make_float2(acc.z, acc.w);
+                    if (d4 == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(big, total_l);
+                }
             } else {
                 float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
                 *reinterpret_cast<float2 *>(dst + d4) = make_float2(acc.x, acc.y);
@@ -776,6 +788,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
 
+        if (nseg == 1 && tid == 0) s_last = 0;
         if (nseg > 1) {
             // Ticket with release/acquire semantics at GPU scope: together with the CTA barriers
             // it orders every thread's state stores before the merging CTA's loads.
@@ -845,6 +858,78 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     store_result(row, d4, acc, big, total_l);
                 }
                 if (tid == 0) p.counters[pair] = 0;  // ready for the next launch
+            }
+        }
+        if (p.cp.world > 0 && (nseg == 1 || s_last)) {
+            // This CTA produced the pair's state on this rank and has stored it to all ranks.
+            // Raise the pair's flag everywhere, wait (bounded) for the same pair from every rank,
+            // then merge the ranks' states of these rows and write the final output.
+            const uint32_t parity = p.cp.step & 1u;
+            const size_t flag_index = (static_cast<size_t>(parity) * kCpMaxWorld) * num_pairs + pair;
+            __threadfence_system();
+            __syncthreads();
+            if (tid < p.cp.world) {
+                __threadfence_system();
+                unsigned *flag = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(p.cp.bases[tid]) +
+                                                              p.cp.flags_offset) +
+                                 flag_index + static_cast<size_t>(p.cp.rank) * num_pairs;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.cp.step) : "memory");
+                const unsigned *mine = reinterpret_cast<const unsigned *>(
+                                           reinterpret_cast<const char *>(p.cp.bases[p.cp.rank]) + p.cp.flags_offset) +
+                                       flag_index + static_cast<size_t>(tid) * num_pairs;
+                const unsigned long long t0 = global_timer_ns();
+                unsigned seen;
+                while (true) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                    if (seen == p.cp.step) break;
+                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                        atomicOr(p.status, SA_DEV_PIPELINE_TIMEOUT);
+                        break;
+                    }
+                    __nanosleep(32);
+                }
+            }
+            __syncthreads();
+            const float *gather = reinterpret_cast<const float *>(p.cp.bases[p.cp.rank]) +
+                                  parity * p.cp.gather_floats_per_parity;
+            const size_t rank_stride = static_cast<size_t>(p.batch) * p.q_heads * STATE_STRIDE;
+            for (int item = tid; item < items; item += NTHREADS) {
+                const int row = item / (D / 4);
+                const int d4 = (item - row * (D / 4)) * 4;
+                const float *row0 = gather + (out_row0 + row) * STATE_STRIDE;
+                float2 ml[kCpFuseWorld], lo2[kCpFuseWorld], hi2[kCpFuseWorld];
+#pragma unroll
+                for (int r = 0; r < kCpFuseWorld; ++r) {  // every load of the row issued before first use
+                    if (r < p.cp.world) {
+                        const float *st = row0 + r * rank_stride;
+                        ml[r] = __ldcg(reinterpret_cast<const float2 *>(st + D));
+                        lo2[r] = __ldcg(reinterpret_cast<const float2 *>(st + d4));
+                        hi2[r] = __ldcg(reinterpret_cast<const float2 *>(st + d4 + 2));
+                    } else {
+                        ml[r] = make_float2(-INFINITY, 0.0f);
+                        lo2[r] = make_float2(0.0f, 0.0f);
+                        hi2[r] = make_float2(0.0f, 0.0f);
+                    }
+                }
+                float big = -INFINITY;
+#pragma unroll
+                for (int r = 0; r < kCpFuseWorld; ++r)
+                    if (ml[r].y > 0.0f) big = fmaxf(big, ml[r].x);
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float total_l = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kCpFuseWorld; ++r) {
+                    const float wgt = ml[r].y > 0.0f ? exp2_diff(ml[r].x, big) : 0.0f;
+                    acc.x += wgt * lo2[r].x;
+                    acc.y += wgt * lo2[r].y;
+                    acc.z += wgt * hi2[r].x;
+                    acc.w += wgt * hi2[r].y;
+                    total_l += wgt * ml[r].y;
+                }
+                const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
+                T *dst = static_cast<T *>(p.cp.final_out) + (out_row0 + row) * D + d4;
+                *reinterpret_cast<uint2 *>(dst) =
+                    make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
             }
         }
         __syncthreads();  // the state areas and s_last are reused by the next segment
@@ -917,7 +1002,7 @@ size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch)
            (static_cast<size_t>(batch) + 1) * 4 + 16;
 }
 
-cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream)
+cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpFuse &cp, cudaStream_t stream)
 {
     StreamParams sp;
     sp.q = p.q;
@@ -944,6 +1029,7 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStrea
     sp.tok_dim = geo.tok_dim;
     sp.uniform_tiles = geo.uniform_tiles;
     sp.seq = p.seq;
+    sp.cp = cp;
 #ifdef SA_TIMELINE
     sp.timeline = g_timeline;
 #endif

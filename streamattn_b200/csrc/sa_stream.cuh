@@ -8,6 +8,21 @@ namespace sa {
 constexpr int kStreamWarps = 4;
 constexpr int kStreamStages = 3;
 
+constexpr int kCpMaxWorld = SA_CP_MAX_WORLD;
+constexpr int kCpFuseWorld = 8;  // ranks the fused decode+exchange launch supports (one NVSwitch box)
+
+// Context-parallel exchange fused into the decode launch: where the ranks' gather buffers are.
+//   gather[2][world][rows][D+2] float, then flags[2][kCpMaxWorld][pairs] uint32 at flags_offset.
+struct CpFuse {
+    int world;  // 0 = not a context-parallel launch
+    int rank;
+    uint32_t step;
+    uint64_t bases[kCpMaxWorld];
+    unsigned long long gather_floats_per_parity;
+    unsigned long long flags_offset;
+    void *final_out;  // [batch, q_heads, D] in the query dtype
+};
+
 struct StreamGeometry {
     CUtensorMap map_k;
     CUtensorMap map_v;
@@ -23,6 +38,6 @@ int stream_tile_tokens(int head_dim);
 int stream_stages(int head_dim, bool rows16);
 size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch);
 constexpr size_t kStreamSmemLimit = 227 * 1024 - 64;
-cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, cudaStream_t stream);
+cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpFuse &cp, cudaStream_t stream);
 
 }  // namespace sa

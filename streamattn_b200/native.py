@@ -68,6 +68,9 @@ _SIGNATURES = {
     "sa_cp_exchange_bytes": ([_i, _i64, _i], _sz),
     "sa_cp_exchange_merge": ([_vp, ctypes.POINTER(ctypes.c_uint64), _i, _i, ctypes.c_uint32, _i64, _i, _vp, _i, _vp], _i),
     "sa_cp_exchange_status": ([_vp, _i, _i64, _i, _vp], _i),
+    "sa_cp_fused_bytes": ([_i, _i, _i, _i, _i], _sz),
+    "sa_cp_fused_plan_create": ([_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
+                                 _i, _i, ctypes.POINTER(ctypes.c_uint64), _i, _i], _vp),
     "sa_exact_plan_create": (_EXACT_ARGS, _vp),
     "sa_paged_plan_create": (_PAGED_ARGS, _vp),
     "sa_seed_plan_create": (_SEED_COMMON + [_i, _i32p, _i, _i, _i], _vp),
@@ -467,3 +470,33 @@ class PeerExchange:
         if rc < 0:
             raise RuntimeError(last_error())
         return rc
+
+
+def cp_fused_bytes(world_size: int, batch: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
+    n = int(load().sa_cp_fused_bytes(world_size, batch, q_heads, kv_heads, head_dim))
+    if n == 0:
+        raise ValueError(last_error())
+    return n
+
+
+def cp_fused_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
+                  workspace: torch.Tensor, peer_buffer_ptrs: Sequence[int], rank: int, *,
+                  kv_layout: str = "BHND", num_ctas: int = 0) -> NativePlan:
+    """One-launch context-parallel step: shard decode + peer exchange + cross-rank merge."""
+
+    device = require_cuda(query, key, value, output, workspace)
+    if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query/key/value must share a dtype of bf16 or fp16")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, value, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    _check_output(output, query, False)
+    world = len(peer_buffer_ptrs)
+    ptrs = (ctypes.c_uint64 * world)(*[int(x) for x in peer_buffer_ptrs])
+    with torch.cuda.device(device):
+        handle = load().sa_cp_fused_plan_create(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(workspace), workspace.numel(),
+            batch, q_heads, kv_heads, dim, kv_len, q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+            int(num_ctas), ptrs, world, int(rank),
+        )
+    return NativePlan(handle, device, (query, key, value, output, workspace))

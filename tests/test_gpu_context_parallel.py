@@ -67,7 +67,7 @@ def _worker(rank: int, world: int, port: int, exchange: str, results) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+@pytest.mark.parametrize("exchange", ["fused", "peer", "nccl"])
 def test_context_parallel_two_ranks(exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -99,10 +99,11 @@ def test_peer_exchange_kernel_world_size_one():
 
         kh = k.permute(0, 2, 1, 3).contiguous().to(dev)
         vh = v.permute(0, 2, 1, 3).contiguous().to(dev)
-        cp = ContextParallelExactDecode(q.to(dev), kh, vh, exchange="peer")
-        assert cp.exchange == "peer" and cp.launches_per_run == 2
-        for _ in range(3):
-            _close(cp.run(), want)
-        assert cp.device_status() == 0
+        for exchange, launches in (("peer", 2), ("fused", 1)):
+            cp = ContextParallelExactDecode(q.to(dev), kh, vh, exchange=exchange)
+            assert cp.exchange == exchange and cp.launches_per_run == launches
+            for _ in range(3):
+                _close(cp.run(), want)
+            assert cp.device_status() == 0
     finally:
         dist.destroy_process_group()
