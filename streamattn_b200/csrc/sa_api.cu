@@ -577,10 +577,12 @@ struct FusedLayout {
 
 FusedLayout fused_layout(int world, int batch, int q_heads, int kv_heads, int head_dim)
 {
+    // gather[2][world][rows][D+2] of 8-byte {value, step} words; no separate flags.
+    (void)kv_heads;
     FusedLayout l;
     l.gather_floats_per_parity = static_cast<size_t>(world) * batch * q_heads * (head_dim + 2);
-    l.flags_offset = (2 * l.gather_floats_per_parity * 4 + 127) / 128 * 128;
-    l.total_bytes = l.flags_offset + 2ull * kCpMaxWorld * batch * kv_heads * 4;
+    l.flags_offset = (2 * l.gather_floats_per_parity * 8 + 127) / 128 * 128;
+    l.total_bytes = l.flags_offset + 128;
     return l;
 }
 

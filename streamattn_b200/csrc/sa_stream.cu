@@ -153,6 +153,20 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, u
                  : "r"(addr));
 }
 
+// Context-parallel exchange words: {value, step} written and read as one 8-byte access.
+__device__ __forceinline__ void cp_store(uint2 *dst, float value, uint32_t step)
+{
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(value)), "r"(step)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint2 cp_load(const uint2 *src)
+{
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
+    return v;
+}
+
 template <typename T> struct Mma;
 template <> struct Mma<__nv_bfloat16> {
     __device__ __forceinline__ static void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
@@ -184,6 +198,116 @@ template <> struct Mma<__half> {
         return *reinterpret_cast<uint32_t *>(&v);
     }
 };
+
+// Copy the tagged words of one pair's state rows (`words` contiguous 8-byte words at word offset
+// `start` of every rank's buffer) from this rank's own buffer to all peers.  Consecutive lanes
+// move consecutive 16-byte pieces, so one warp store covers 512 contiguous bytes: small scattered
+// stores are what NVLink handles worst.  Each 8-byte half carries its own step tag, so the copy
+// needs no ordering or atomicity beyond that of an aligned 8-byte access.
+template <int NTHREADS>
+__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, size_t start, int words, int tid)
+{
+    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint2 *>(cp.bases[cp.rank]) + start);
+    for (int i = tid; i < words / 2; i += NTHREADS) {  // `start` and `words` are even: 16-byte pieces
+        const uint4 v = __ldcg(src + i);
+        for (int r = 0; r < cp.world; ++r) {
+            if (r == cp.rank) continue;
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[r]) + start) + i;
+            asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y),
+                         "r"(v.z), "r"(v.w)
+                         : "memory");
+        }
+    }
+}
+
+// Context-parallel finish of one (row, kv head) pair, run by the CTA that completed the pair on
+// this rank after it stored the pair's state rows to every rank: wait (bounded) for the same rows
+// from all ranks - each 8-byte word carries the step number, so the data is its own flag - then
+// merge them exactly and write the final output rows.  Kept out of line so its registers do not
+// weigh on the streaming loop.
+template <typename T, int D, int NTHREADS>
+__device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_t total_rows, int64_t out_row0,
+                                            int items, int tid)
+{
+    constexpr int STATE_STRIDE = D + 2;
+    const uint2 *gather = reinterpret_cast<const uint2 *>(cp.bases[cp.rank]) + (cp.step & 1u) * cp.gather_floats_per_parity;
+    const size_t rank_stride = total_rows * STATE_STRIDE;
+    for (int item = tid; item < items; item += NTHREADS) {
+        const int row = item / (D / 4);
+        const int d4 = (item - row * (D / 4)) * 4;
+        const uint2 *row0 = gather + (out_row0 + row) * STATE_STRIDE;
+        const unsigned long long t0 = global_timer_ns();
+        // (m, l) of every rank first: they fix the weights.
+        float m[kCpFuseWorld], l[kCpFuseWorld];
+        bool waiting = true;
+        while (waiting) {
+            waiting = false;
+#pragma unroll
+            for (int r = 0; r < kCpFuseWorld; ++r) {
+                if (r < cp.world) {
+                    const uint2 wm = cp_load(row0 + r * rank_stride + D);
+                    const uint2 wl = cp_load(row0 + r * rank_stride + D + 1);
+                    m[r] = __uint_as_float(wm.x);
+                    l[r] = __uint_as_float(wl.x);
+                    waiting |= wm.y != cp.step || wl.y != cp.step;
+                } else {
+                    m[r] = -INFINITY;
+                    l[r] = 0.0f;
+                }
+            }
+            if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
+                break;
+            }
+        }
+        float big = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < kCpFuseWorld; ++r)
+            if (l[r] > 0.0f) big = fmaxf(big, m[r]);
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float total_l = 0.0f;
+        // Then the four columns of this item, four ranks at a time.
+#pragma unroll
+        for (int r0 = 0; r0 < kCpFuseWorld; r0 += 4) {
+            if (r0 >= cp.world) break;
+            uint2 w[4][4];
+            waiting = true;
+            while (waiting) {
+                waiting = false;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (r0 + i < cp.world) {
+                        const uint2 *st = row0 + (r0 + i) * rank_stride + d4;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            w[i][j] = cp_load(st + j);
+                            waiting |= w[i][j].y != cp.step;
+                        }
+                    }
+                }
+                if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
+                    atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
+                    break;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (r0 + i < cp.world) {
+                    const float wgt = l[r0 + i] > 0.0f ? exp2_diff(m[r0 + i], big) : 0.0f;
+                    acc.x += wgt * __uint_as_float(w[i][0].x);
+                    acc.y += wgt * __uint_as_float(w[i][1].x);
+                    acc.z += wgt * __uint_as_float(w[i][2].x);
+                    acc.w += wgt * __uint_as_float(w[i][3].x);
+                    total_l += wgt * l[r0 + i];
+                }
+            }
+        }
+        const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
+        T *dst = static_cast<T *>(cp.final_out) + (out_row0 + row) * D + d4;
+        *reinterpret_cast<uint2 *>(dst) =
+            make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
+    }
+}
 
 // One fragment (TMA box) of a tile as seen by the issuing lane.
 struct Frag {
@@ -742,14 +866,21 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
             } else if (p.cp.world > 0) {
                 // Context-parallel: this rank's state row goes straight into every rank's gather
-                // buffer (plain peer stores over NVLink, own copy included).
+                // buffer (plain peer stores over NVLink, own copy included).  Every value travels
+                // as an 8-byte word {value, step}: the word is written atomically, so a reader that
+                // sees the step number also sees the value - no fence or separate flag round trip.
                 const size_t off = (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
                                    (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0 + row) * STATE_STRIDE;
-                for (int r = 0; r < p.cp.world; ++r) {
-                    float *dst = reinterpret_cast<float *>(p.cp.bases[r]) + off;
-                    *reinterpret_cast<float2 *>(dst + d4) = make_float2(acc.x, acc.y);
-                    *reinterpret_cast<float2 *>(dst + d4 + 2) = make_float2(acc.z, acc.w);
-                    if (d4 == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(big, total_l);
+                // Here only this rank's own buffer is written; cp_broadcast_pair() then copies the
+                // pair's rows to the peers with wide, lane-contiguous stores.
+                uint2 *dst = reinterpret_cast<uint2 *>(p.cp.bases[p.cp.rank]) + off;
+                cp_store(dst + d4, acc.x, p.cp.step);
+                cp_store(dst + d4 + 1, acc.y, p.cp.step);
+                cp_store(dst + d4 + 2, acc.z, p.cp.step);
+                cp_store(dst + d4 + 3, acc.w, p.cp.step);
+                if (d4 == 0) {
+                    cp_store(dst + D, big, p.cp.step);
+                    cp_store(dst + D + 1, total_l, p.cp.step);
                 }
             } else {
                 float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
@@ -861,77 +992,15 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
         if (p.cp.world > 0 && (nseg == 1 || s_last)) {
-            // This CTA produced the pair's state on this rank and has stored it to all ranks.
-            // Raise the pair's flag everywhere, wait (bounded) for the same pair from every rank,
-            // then merge the ranks' states of these rows and write the final output.
-            const uint32_t parity = p.cp.step & 1u;
-            const size_t flag_index = (static_cast<size_t>(parity) * kCpMaxWorld) * num_pairs + pair;
-            __threadfence_system();
-            __syncthreads();
-            if (tid < p.cp.world) {
-                __threadfence_system();
-                unsigned *flag = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(p.cp.bases[tid]) +
-                                                              p.cp.flags_offset) +
-                                 flag_index + static_cast<size_t>(p.cp.rank) * num_pairs;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.cp.step) : "memory");
-                const unsigned *mine = reinterpret_cast<const unsigned *>(
-                                           reinterpret_cast<const char *>(p.cp.bases[p.cp.rank]) + p.cp.flags_offset) +
-                                       flag_index + static_cast<size_t>(tid) * num_pairs;
-                const unsigned long long t0 = global_timer_ns();
-                unsigned seen;
-                while (true) {
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-                    if (seen == p.cp.step) break;
-                    if (global_timer_ns() - t0 > kWaitLimitNs) {
-                        atomicOr(p.status, SA_DEV_PIPELINE_TIMEOUT);
-                        break;
-                    }
-                    __nanosleep(32);
-                }
-            }
-            __syncthreads();
-            const float *gather = reinterpret_cast<const float *>(p.cp.bases[p.cp.rank]) +
-                                  parity * p.cp.gather_floats_per_parity;
-            const size_t rank_stride = static_cast<size_t>(p.batch) * p.q_heads * STATE_STRIDE;
-            for (int item = tid; item < items; item += NTHREADS) {
-                const int row = item / (D / 4);
-                const int d4 = (item - row * (D / 4)) * 4;
-                const float *row0 = gather + (out_row0 + row) * STATE_STRIDE;
-                float2 ml[kCpFuseWorld], lo2[kCpFuseWorld], hi2[kCpFuseWorld];
-#pragma unroll
-                for (int r = 0; r < kCpFuseWorld; ++r) {  // every load of the row issued before first use
-                    if (r < p.cp.world) {
-                        const float *st = row0 + r * rank_stride;
-                        ml[r] = __ldcg(reinterpret_cast<const float2 *>(st + D));
-                        lo2[r] = __ldcg(reinterpret_cast<const float2 *>(st + d4));
-                        hi2[r] = __ldcg(reinterpret_cast<const float2 *>(st + d4 + 2));
-                    } else {
-                        ml[r] = make_float2(-INFINITY, 0.0f);
-                        lo2[r] = make_float2(0.0f, 0.0f);
-                        hi2[r] = make_float2(0.0f, 0.0f);
-                    }
-                }
-                float big = -INFINITY;
-#pragma unroll
-                for (int r = 0; r < kCpFuseWorld; ++r)
-                    if (ml[r].y > 0.0f) big = fmaxf(big, ml[r].x);
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                float total_l = 0.0f;
-#pragma unroll
-                for (int r = 0; r < kCpFuseWorld; ++r) {
-                    const float wgt = ml[r].y > 0.0f ? exp2_diff(ml[r].x, big) : 0.0f;
-                    acc.x += wgt * lo2[r].x;
-                    acc.y += wgt * lo2[r].y;
-                    acc.z += wgt * hi2[r].x;
-                    acc.w += wgt * hi2[r].y;
-                    total_l += wgt * ml[r].y;
-                }
-                const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
-                T *dst = static_cast<T *>(p.cp.final_out) + (out_row0 + row) * D + d4;
-                *reinterpret_cast<uint2 *>(dst) =
-                    make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
-            }
+            __syncthreads();  // the pair's rows are complete in this rank's own buffer
+            cp_broadcast_pair<NTHREADS>(
+                p.cp,
+                (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
+                    (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0) * STATE_STRIDE,
+                group * STATE_STRIDE, tid);
         }
+        if (p.cp.world > 0 && (nseg == 1 || s_last))
+            cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, static_cast<size_t>(p.batch) * p.q_heads, out_row0, items, tid);
         __syncthreads();  // the state areas and s_last are reused by the next segment
         SA_STAMP(6);
         cur = seg_end;

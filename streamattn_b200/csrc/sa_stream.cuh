@@ -12,7 +12,7 @@ constexpr int kCpMaxWorld = SA_CP_MAX_WORLD;
 constexpr int kCpFuseWorld = 8;  // ranks the fused decode+exchange launch supports (one NVSwitch box)
 
 // Context-parallel exchange fused into the decode launch: where the ranks' gather buffers are.
-//   gather[2][world][rows][D+2] float, then flags[2][kCpMaxWorld][pairs] uint32 at flags_offset.
+//   gather[2][world][rows][D+2] of 8-byte words {float bits, step}; gather_floats_per_parity counts words.
 struct CpFuse {
     int world;  // 0 = not a context-parallel launch
     int rank;
