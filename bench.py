@@ -12,7 +12,7 @@ Workloads (BASELINE.json configs):
   paged_c3   paged HND page-16, ragged lengths U[16384, 65536], random page order
   seed_c4    seed-only decode, Qwen2.5-3B attention shape, 384 seed tokens of 32768
   cp_c5      context-parallel exact decode, B1 Hq32 Hkv8 D128 N1048576 sharded over N GPUs
-             (strong scaling; state all-gather over NCCL + merge)                       [default at N>1]
+             (strong scaling; state exchange fused into the decode kernel over peer memory) [default at N>1]
 
 Under torchrun (N>1) every rank runs; timing is the max over ranks of CUDA-event
 time between a barrier + synchronize on both sides.  ``--impl reference`` times the
