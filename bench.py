@@ -132,6 +132,18 @@ def _randn_bf16(shape, seed, device):
 # Workloads: each returns (run_fn, q_device, out_device, info)
 # --------------------------------------------------------------------------
 
+SCHEDULE = {"dynamic": None}  # set from --schedule: None follows STREAMATTN_B200_SCHEDULE (default static)
+
+
+def schedule_name(workload: str) -> str:
+    from streamattn_b200 import native
+
+    if workload not in ("exact_c2", "exact_c2_bnhd", "paged_c3"):
+        return "static"
+    dynamic = SCHEDULE["dynamic"] if SCHEDULE["dynamic"] is not None else native.dynamic_default()
+    return "dynamic (tiles claimed from a device counter; not bit-reproducible)" if dynamic else "static"
+
+
 def build_exact_c2(device, layout="BHND"):
     import streamattn_b200 as sa
 
@@ -141,7 +153,7 @@ def build_exact_c2(device, layout="BHND"):
     v = _randn_bf16((B, Hkv, N, D), 2, device)
     if layout == "BNHD":
         k, v = k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous()
-    plan = sa.ExactDecodePlan.build(q, k, v, kv_layout=layout)
+    plan = sa.ExactDecodePlan.build(q, k, v, kv_layout=layout, dynamic_schedule=SCHEDULE["dynamic"])
     info = dict(workload="exact_c2" if layout == "BHND" else "exact_c2_bnhd", batch=B, q_heads=Hq, kv_heads=Hkv,
                 head_dim=D, kv_len=N, kv_layout=layout, kernel=plan.kernel_name, ctas=plan.num_ctas,
                 bytes=2 * B * Hkv * N * D * 2, launches=plan.launches_per_run)
@@ -164,7 +176,7 @@ def build_paged_c3(device):
         table[b, -(-int(lengths[b]) // page):] = -1
     cache = sa.PagedKVCache(key=k, value=v, page_table=table.to(device), sequence_lengths=lengths.to(device),
                             layout="HND")
-    plan = sa.PagedExactDecodePlan.build(q, cache)
+    plan = sa.PagedExactDecodePlan.build(q, cache, dynamic_schedule=SCHEDULE["dynamic"])
     tokens = int(lengths.sum())
     pages = int(sum(-(-int(n) // page) for n in lengths))
     info = dict(workload="paged_c3", batch=B, q_heads=Hq, kv_heads=Hkv, head_dim=D, page_size=page, capacity=cap,
@@ -287,9 +299,13 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "peer", "nccl"],
                     help="cp_c5 only: how the per-rank states meet (fused peer-store kernel or NCCL all-gather)")
+    ap.add_argument("--schedule", default="default", choices=["default", "static", "dynamic"],
+                    help="tile schedule of the exact/paged plans: static is bit-reproducible (the default), "
+                         "dynamic claims tiles from a device counter")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + the timed region (for runs under ncu): no e2e, CPU or clock legs")
     args = ap.parse_args()
+    SCHEDULE["dynamic"] = {"default": None, "static": False, "dynamic": True}[args.schedule]
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -452,7 +468,8 @@ def main() -> None:
             "steps": args.steps, "warmup": warmup, "ms_per_step": step_s * 1e3, "us_per_call": step_s * 1e6,
             "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {**info, "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2"),
+            "config": {**info, "schedule": schedule_name(workload),
+                       "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2"),
                        "timing": "CUDA events around K back-to-back calls, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(workload),

@@ -50,6 +50,14 @@ enum sa_page_layout { SA_LAYOUT_NHD = 0, SA_LAYOUT_HND = 1 };
 enum sa_block_order { SA_ORDER_SEQUENTIAL = 0, SA_ORDER_RECENT_FIRST = 1, SA_ORDER_SINK_RECENT_FIRST = 2 };
 enum sa_out_mode { SA_OUT_FINAL = 0, SA_OUT_STATE = 1 };
 enum sa_kernel_choice { SA_KERNEL_AUTO = 0, SA_KERNEL_STREAM = 1, SA_KERNEL_GENERIC = 2 };
+/* May be OR-ed into any kernel_choice argument.  The streaming kernel then lets the CTAs that
+   share a (row, KV head) pair claim their tiles from a device counter instead of owning a fixed
+   slice, which evens out SMs that the memory system serves at different rates (a few percent
+   faster on HBM-bound calls).  The split states are then grouped differently from launch to
+   launch, so results agree within the float tolerance but are not bit-reproducible; without
+   the flag every call with the same inputs returns the same bits.  Ignored where it does not
+   apply (generic kernel, fewer than four CTAs per pair, very long rows). */
+#define SA_KERNEL_FLAG_DYNAMIC 0x100
 
 /* Bits of the device status word (sa_workspace_status). */
 enum sa_device_status {

@@ -40,7 +40,8 @@ int generic_splits_bound(int64_t pairs, int num_ctas)
     return static_cast<int>(s);
 }
 
-size_t counters_bytes(int batch, int q_heads) { return round_up(static_cast<size_t>(batch) * q_heads * 4, 256); }
+// Arrival counters [batch*q_heads] followed by the dynamic schedule's claim counters [batch*q_heads].
+size_t counters_bytes(int batch, int q_heads) { return round_up(static_cast<size_t>(batch) * q_heads * 8, 256); }
 
 size_t stream_partial_floats(int batch, int q_heads, int kv_heads, int head_dim, int ctas)
 {
@@ -209,10 +210,17 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
         ctas = std::min<int64_t>(p.num_ctas, kMaxCtas);
     } else {
         const int sm = p.sm_count > 0 ? std::min(p.sm_count, kMaxAutoCtas) : 148;
-        ctas = std::min<int64_t>(sm, (tiles + kStreamWarps - 1) / kStreamWarps);
+        // Small problems are latency-bound: spread them over many CTAs (four tiles each, so
+        // half of a CTA's warps may stay idle) rather than filling every warp of a few CTAs.
+        constexpr int kMinTilesPerCta = 4;
+        ctas = std::min<int64_t>(sm, (tiles + kMinTilesPerCta - 1) / kMinTilesPerCta);
     }
     ctas = std::max<int64_t>(1, std::min<int64_t>(ctas, tiles));
     geo->num_ctas = static_cast<int>(ctas);
+    // Token-major caches ([.., token, head, D]: BNHD, paged NHD) interleave the heads' rows in
+    // memory: there the CTAs of a pair take tiles round-robin, so all heads of a row sweep the
+    // same addresses together; head-major caches give every CTA one contiguous slice.
+    geo->schedule = geo->tok_dim == 2 ? kScheduleCyclic : kScheduleBlocked;
     return true;
 }
 
@@ -226,7 +234,8 @@ int check_common(const void *q, const void *k, const void *v, const void *out, c
     if (dtype < SA_DTYPE_BF16 || dtype > SA_DTYPE_F32) return fail(SA_ERR_INVALID, "unknown dtype");
     if (out_mode != SA_OUT_FINAL && out_mode != SA_OUT_STATE) return fail(SA_ERR_INVALID, "unknown out_mode");
     if (num_ctas < 0) return fail(SA_ERR_INVALID, "num_ctas must be >= 0");
-    if (kernel_choice < SA_KERNEL_AUTO || kernel_choice > SA_KERNEL_GENERIC)
+    const int base_choice = kernel_choice & ~SA_KERNEL_FLAG_DYNAMIC;
+    if (base_choice < SA_KERNEL_AUTO || base_choice > SA_KERNEL_GENERIC)
         return fail(SA_ERR_INVALID, "unknown kernel_choice");
     if (static_cast<int64_t>(batch) * q_heads > 1 << 24) return fail(SA_ERR_UNSUPPORTED, "too many (row, head) pairs");
     return SA_OK;
@@ -250,10 +259,13 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
 
     const char *why = "";
     plan->use_stream = false;
+    const bool dynamic = (kernel_choice & SA_KERNEL_FLAG_DYNAMIC) != 0;
+    kernel_choice &= ~SA_KERNEL_FLAG_DYNAMIC;
     if (kernel_choice != SA_KERNEL_GENERIC) {
         plan->use_stream = build_stream_geometry(p, max_vlen, &plan->geo, &why);
         if (!plan->use_stream && kernel_choice == SA_KERNEL_STREAM)
             return fail(SA_ERR_UNSUPPORTED, "streaming kernel does not cover this call: %s", why);
+        if (plan->use_stream && dynamic) plan->geo.schedule = kScheduleClaims;
     }
     size_t need;
     if (plan->use_stream) {

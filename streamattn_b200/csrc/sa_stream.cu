@@ -25,7 +25,10 @@ extern unsigned long long *g_timeline;
 
 namespace {
 
-constexpr int kTileBytes = 8192;             // one K or one V tile
+#ifndef SA_STREAM_TILE_BYTES
+#define SA_STREAM_TILE_BYTES 8192
+#endif
+constexpr int kTileBytes = SA_STREAM_TILE_BYTES;  // one K or one V tile
 constexpr int kStageBytes = 2 * kTileBytes;  // K + V
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
@@ -36,6 +39,7 @@ struct StreamParams {
     int out_mode;
     float *partials;
     int *counters;
+    int *pool;           // per-pair claim counters of the dynamic schedule (zero between launches)
     int *status;
     int32_t *trace;
     int batch, q_heads, kv_heads, group;
@@ -48,6 +52,7 @@ struct StreamParams {
     int fpu_shift;       // log2(frags_per_unit)
     int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
+    int schedule;        // kScheduleBlocked / kScheduleCyclic / kScheduleClaims
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
@@ -311,6 +316,7 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_
 
 // One fragment (TMA box) of a tile as seen by the issuing lane.
 struct Frag {
+    int x;              // global tile index, -1: no tile (warp-uniform)
     int state;          // 0: nothing to load, 1: load, 2: page id out of range (skip + report)
     int tok;            // token coordinate of the box
     int outer;          // outermost coordinate: batch row or physical page
@@ -341,7 +347,8 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + WARPS * STAGES * kStageBytes);
     float *states = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + BAR_BYTES);
-    int *prefix = reinterpret_cast<int *>(states + WARPS * STATE_FLOATS);
+    int *prefix = reinterpret_cast<int *>(states + WARPS * STATE_FLOATS);  // ragged rows: tiles before row b
+    int *vlens = prefix + p.batch + 1;                                      // ragged rows: length of row b
     __shared__ int s_last;
 
     const int tid = threadIdx.x;
@@ -360,6 +367,13 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     uint8_t *warp_ring = ring + warp * STAGES * kStageBytes;
 
     SA_STAMP(0);
+#if defined(SA_TIMELINE) && SA_TIMELINE == 1
+    if (p.timeline != nullptr && tid == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.timeline[blockIdx.x * 8 + 2] = smid;
+    }
+#endif
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_v)) : "memory");
@@ -376,7 +390,11 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             for (int base = 0; base < p.batch; base += 32) {
                 const int b = base + lane;
                 int x = 0;
-                if (b < p.batch) x = static_cast<int>((row_vlen(p.seq, b) + TILE_N - 1) / TILE_N);
+                if (b < p.batch) {
+                    const int64_t n = row_vlen(p.seq, b);  // < 2^31: the host bounds the capacity
+                    vlens[b] = static_cast<int>(n);
+                    x = static_cast<int>((n + TILE_N - 1) / TILE_N);
+                }
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const int y = __shfl_up_sync(0xffffffffu, x, o);
@@ -398,6 +416,8 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
     // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
     auto tiles_before = [&](int b) -> int { return ragged ? prefix[b] : b * p.uniform_tiles; };
+    // Row lengths were read once for the prefix sum; uniform rows need no load at all.
+    auto vlen_of = [&](int b) -> int64_t { return ragged ? static_cast<int64_t>(vlens[b]) : row_vlen(p.seq, b); };
     const int total_tiles = Hkv * tiles_before(p.batch);
     // CTA c owns tiles [c*q + min(c, r), (c+1)*q + min(c+1, r)) with q = T / C, r = T % C:
     // the first r CTAs take one extra tile.  owner(x) is the CTA that owns tile x.
@@ -438,6 +458,10 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     bool aligned = total_tiles > 0 && 4 * num_pairs <= C &&
                    static_cast<uint64_t>(C) * static_cast<uint64_t>(total_tiles) < (1ull << 32);
     int al_pair = -1, al_start = 0, al_end = 0;  // aligned mode: this CTA's pair and its tile range
+    bool dyn = false;                            // the pair's warps share its tiles (cyclic or claims)
+    bool dyn_claims = false;                     // ... through the claim counter
+    int dyn_chunk = 1;                           // tiles per claim
+    int dyn_nw = 0, dyn_gw = 0;                  // warps working on the pair, this warp's index among them
     if (aligned) {
         // One pair per lane: lane pp computes cs(pp); cs(pp+1) comes from the neighbour lane.
         const unsigned half = static_cast<unsigned>(total_tiles) / 2;
@@ -500,7 +524,22 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             al_nseg = static_cast<int>(n_eff);
             al_start = static_cast<int>(t0);
             al_end = static_cast<int>(t1);
-            if (k < n_eff) {
+            const bool claims = p.schedule == kScheduleClaims;
+            if ((claims || p.schedule == kScheduleCyclic) && n_eff == n_p && tiles_p >= n_p * WARPS * (STAGES + 1)) {
+                // Shared schedules: the pair's warps take tiles round-robin by position - all of
+                // them (cyclic), or only their first STAGES + 1, after which every tile is claimed
+                // from the pair's counter, so a CTA that the memory system serves slowly simply
+                // ends up with fewer tiles.
+                dyn = true;
+                dyn_claims = claims;
+                // One counter serves about 30 claims per microsecond: with many CTAs on a pair a
+                // claim covers several consecutive tiles.
+                dyn_chunk = (static_cast<int>(n_p) + 15) / 16;
+                dyn_nw = static_cast<int>(n_p) * WARPS;
+                dyn_gw = static_cast<int>(k) * WARPS + warp;
+                lo = al_start;
+                hi = al_end;
+            } else if (k < n_eff) {
                 if (tiles_p < (1u << 20)) {  // products fit 32 bits (n_eff <= C <= 4096)
                     lo = static_cast<int>(t0 + tiles_p * k / n_eff);
                     hi = static_cast<int>(t0 + tiles_p * (k + 1) / n_eff);
@@ -516,11 +555,51 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         hi = range_lo(c + 1);
     }
     SA_PSTAMP(3);
-    // This warp's tiles are lo + warp + j*WARPS for j in [0, n_w), across all segments of the CTA,
-    // so its copy pipeline keeps running through segment boundaries.
+    // Static schedule: this warp's tiles are lo + warp + i*WARPS for i in [0, n_w), across all
+    // segments of the CTA, so its copy pipeline keeps running through segment boundaries.
+    // Dynamic schedule: tiles al_start + i*dyn_nw + dyn_gw for i <= STAGES, then one claim per tile.
     const int n_w = hi - lo > warp ? (hi - lo - warp + WARPS - 1) / WARPS : 0;
+    int seq_i = 0;            // tiles of this warp's sequence produced so far
+    int claim = 0;            // lane 0: the claim in flight (dynamic schedule)
+    bool claiming = dyn_claims;  // false once a claim came back past the end of the pair
+    int chunk_x = 0, chunk_left = 0;  // rest of the claimed run of tiles
+    const int dyn_base = al_start + (STAGES + 1) * dyn_nw;
+    auto start_claim = [&]() {
+        if (lane == 0) claim = atomicAdd(p.pool + al_pair, 1);
+    };
+    // Next tile of this warp's sequence (-1: none).  A claim is consumed one call after it was
+    // issued, so the counter's round trip overlaps a whole tile of work.
+    auto next_tile = [&]() -> int {
+        int x = -1;
+        if (!dyn) {
+            if (seq_i < n_w) x = lo + warp + seq_i * WARPS;
+        } else if (seq_i <= STAGES || !dyn_claims) {
+            x = al_start + seq_i * dyn_nw + dyn_gw;
+            if (x >= al_end) x = -1;
+            if (dyn_claims && seq_i == STAGES) start_claim();
+        } else if (chunk_left > 0) {
+            --chunk_left;
+            x = chunk_x++;
+            if (x >= al_end) {
+                x = -1;
+                chunk_left = 0;
+            }
+        } else if (claiming) {
+            x = dyn_base + __shfl_sync(0xffffffffu, claim, 0) * dyn_chunk;
+            if (x < al_end) {
+                chunk_x = x + 1;
+                chunk_left = dyn_chunk - 1;
+                start_claim();
+            } else {
+                x = -1;
+                claiming = false;
+            }
+        }
+        ++seq_i;
+        return x;
+    };
 
-    // What this lane has to copy for the warp's j-th tile (page-table lookups happen here, one
+    // What this lane has to copy for tile x (page-table lookups happen here, one
     // tile before the copies are issued, so their latency stays off the critical path).  The
     // producer keeps its own (row, kv head) cursor: tiles are visited in ascending order, so
     // the cursor only moves when a tile crosses into the next pair.
@@ -531,18 +610,17 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         pc_kvh = al_pair - pc_b * Hkv;
         pc_start = al_start;
         pc_end = al_end;
-        pc_vlen = row_vlen(p.seq, pc_b);
+        pc_vlen = vlen_of(pc_b);
     }
-    auto lookup = [&](int j) -> Frag {
+    auto lookup = [&](int x) -> Frag {
         Frag f;
-        f.state = 0; f.tok = 0; f.outer = 0; f.kvh = 0; f.trace_idx = -1;
-        if (j >= n_w) return f;
-        const int x = lo + warp + j * WARPS;
+        f.x = x; f.state = 0; f.tok = 0; f.outer = 0; f.kvh = 0; f.trace_idx = -1;
+        if (x < 0) return f;
         if (x >= pc_end) {
             int b, row_tiles;
             locate(x, b, pc_kvh, row_tiles, pc_start);
             pc_end = pc_start + row_tiles;
-            if (b != pc_b) pc_vlen = row_vlen(p.seq, b);
+            if (b != pc_b) pc_vlen = vlen_of(b);
             pc_b = b;
         }
         f.kvh = pc_kvh;
@@ -600,11 +678,14 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
     Frag first[STAGES + 1];
 #pragma unroll
-    for (int s = 0; s <= STAGES; ++s) first[s] = lookup(s);  // all table loads in flight together
+    for (int s = 0; s <= STAGES; ++s) first[s] = lookup(next_tile());  // all table loads in flight together
     SA_PSTAMP(4);
+    int xq[STAGES];  // tiles in the ring, oldest first
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s)
-        if (s < n_w) issue(s, first[s]);
+    for (int s = 0; s < STAGES; ++s) {
+        xq[s] = first[s].x;
+        if (xq[s] >= 0) issue(s, first[s]);
+    }
     Frag pending = first[STAGES];
     SA_STAMP(1);
 
@@ -645,7 +726,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         const int pair_end = pair_start + row_tiles;
         const int seg_end = hi < pair_end ? hi : pair_end;
         const int pair = b * Hkv + kvh;
-        const int64_t vlen = row_vlen(p.seq, b);
+        const int64_t vlen = vlen_of(b);
 
         // Query fragments of this KV group (A operand of q.k), rows >= group are zero.
         uint32_t qa[KS_QK][4];
@@ -675,9 +756,9 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             o_acc[i][3] = 0.0f;
         }
 
-        for (; j < n_w; ++j) {
-            const int x = lo + warp + j * WARPS;
-            if (x >= seg_end) break;
+        for (;; ++j) {
+            const int x = xq[0];
+            if (x < 0 || x >= seg_end) break;
             const int lt = x - pair_start;
             const uint32_t slot = static_cast<uint32_t>(j) % STAGES;
             const uint32_t parity = (static_cast<uint32_t>(j) / STAGES) & 1u;
@@ -688,7 +769,15 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 atomicOr(p.status, SA_DEV_PIPELINE_TIMEOUT);
             }
             dead = __any_sync(0xffffffffu, dead);
-            if (dead) continue;
+            if (dead) {  // drop everything that is left; the status word tells the caller
+#pragma unroll
+                for (int s = 0; s < STAGES; ++s) xq[s] = -1;
+                pending.x = -1;
+                claiming = false;
+                chunk_left = 0;
+                seq_i = n_w;
+                break;
+            }
             if (j == 0) SA_STAMP(7);
 
             const int64_t tile_tok0 = static_cast<int64_t>(lt) * TILE_N;
@@ -817,8 +906,11 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             // Order this warp's shared-memory accesses before the async-proxy writes of the refill.
             fence_proxy_async();
             __syncwarp();
-            if (j + STAGES < n_w) issue(j + STAGES, pending);
-            pending = lookup(j + STAGES + 1);
+            if (pending.x >= 0) issue(j + STAGES, pending);
+#pragma unroll
+            for (int s = 0; s + 1 < STAGES; ++s) xq[s] = xq[s + 1];
+            xq[STAGES - 1] = pending.x;
+            pending = lookup(next_tile());
         }
 
         SA_STAMP(3);
@@ -919,7 +1011,10 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
 
-        if (nseg == 1 && tid == 0) s_last = 0;
+        if (nseg == 1 && tid == 0) {
+            s_last = 0;
+            if (dyn_claims) p.pool[pair] = 0;  // every warp of the only CTA has made its last claim
+        }
         if (nseg > 1) {
             // Ticket with release/acquire semantics at GPU scope: together with the CTA barriers
             // it orders every thread's state stores before the merging CTA's loads.
@@ -988,7 +1083,10 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     }
                     store_result(row, d4, acc, big, total_l);
                 }
-                if (tid == 0) p.counters[pair] = 0;  // ready for the next launch
+                if (tid == 0) {  // ready for the next launch: every CTA of the pair has arrived
+                    p.counters[pair] = 0;
+                    if (dyn_claims) p.pool[pair] = 0;
+                }
             }
         }
         if (p.cp.world > 0 && (nseg == 1 || s_last)) {
@@ -1043,7 +1141,7 @@ cudaError_t launch_dim(const CUtensorMap &mk, const CUtensorMap &mv, const Strea
 {
     if (rows16) {
         // 16 head rows at D128 need 33 KB of state areas: two ring stages instead of three.
-        constexpr int kStages16 = D == 128 ? 2 : kStreamStages;
+        constexpr int kStages16 = (D == 128 && kStreamStages > 2) ? 2 : kStreamStages;
         return launch_instance<T, D, kStreamWarps, kStages16, true>(mk, mv, sp, ctas, batch, stream);
     }
     return launch_instance<T, D, kStreamWarps, kStreamStages, false>(mk, mv, sp, ctas, batch, stream);
@@ -1061,14 +1159,17 @@ extern "C" __attribute__((visibility("default"))) void sa_debug_timeline(void *p
 
 int stream_tile_tokens(int head_dim) { return kTileBytes / (head_dim * 2); }
 
-int stream_stages(int head_dim, bool rows16) { return (head_dim == 128 && rows16) ? 2 : kStreamStages; }
+int stream_stages(int head_dim, bool rows16)
+{
+    return (head_dim == 128 && rows16 && kStreamStages > 2) ? 2 : kStreamStages;
+}
 
 size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch)
 {
     const size_t bars = (static_cast<size_t>(kStreamWarps) * stages * 8 + 15) / 16 * 16;
     const size_t states = static_cast<size_t>(kStreamWarps) * (rows16 ? 16 : 8) * (head_dim + 2) * 4;
     return 1024 + static_cast<size_t>(kStreamWarps) * stages * kStageBytes + bars + states +
-           (static_cast<size_t>(batch) + 1) * 4 + 16;
+           (2 * static_cast<size_t>(batch) + 1) * 4 + 16;
 }
 
 cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpFuse &cp, cudaStream_t stream)
@@ -1081,6 +1182,7 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpF
     sp.out_mode = p.out_mode;
     sp.partials = p.ws.partials;
     sp.counters = p.ws.counters;
+    sp.pool = p.ws.counters + static_cast<size_t>(p.batch) * p.q_heads;
     sp.status = p.ws.status;
     sp.trace = p.trace;
     sp.batch = p.batch;
@@ -1097,6 +1199,7 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpF
     sp.fpu_shift = log2i(geo.frags_per_unit);
     sp.tok_dim = geo.tok_dim;
     sp.uniform_tiles = geo.uniform_tiles;
+    sp.schedule = geo.schedule;
     sp.seq = p.seq;
     sp.cp = cp;
 #ifdef SA_TIMELINE

@@ -5,11 +5,25 @@
 
 namespace sa {
 
-constexpr int kStreamWarps = 4;
-constexpr int kStreamStages = 3;
+#ifndef SA_STREAM_WARPS
+#define SA_STREAM_WARPS 8
+#endif
+constexpr int kStreamWarps = SA_STREAM_WARPS;    // each with its own ring of tiles
+#ifndef SA_STREAM_STAGES
+#define SA_STREAM_STAGES 1
+#endif
+constexpr int kStreamStages = SA_STREAM_STAGES;  // 16 KB K+V tiles in flight per warp
 
 constexpr int kCpMaxWorld = SA_CP_MAX_WORLD;
 constexpr int kCpFuseWorld = 8;  // ranks the fused decode+exchange launch supports (one NVSwitch box)
+
+// How the CTAs that share one (row, kv head) pair divide its tiles (pairs with at least four
+// CTAs each; otherwise the tile list is cut into equal slices regardless of pair boundaries).
+enum StreamSchedule : int {
+    kScheduleBlocked = 0,  // one contiguous slice per CTA
+    kScheduleCyclic = 1,   // tiles dealt round-robin to the pair's warps
+    kScheduleClaims = 2,   // first tiles round-robin, then one claim per tile from a device counter
+};
 
 // Context-parallel exchange fused into the decode launch: where the ranks' gather buffers are.
 //   gather[2][world][rows][D+2] of 8-byte words {float bits, step}; gather_floats_per_parity counts words.
@@ -32,6 +46,7 @@ struct StreamGeometry {
     int tok_dim;         // TMA coordinate carrying the token index (1 or 2)
     int uniform_tiles;   // tiles per row if all rows are equally long, else -1
     int num_ctas;
+    int schedule;        // how the CTAs of one (row, kv head) pair share its tiles (kSchedule*)
 };
 
 int stream_tile_tokens(int head_dim);

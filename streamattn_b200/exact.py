@@ -50,7 +50,8 @@ class ExactDecodePlan:
     def build(cls, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, *,
               output: Optional[torch.Tensor] = None, num_splits: Optional[int] = None,
               promoted_only: bool = True, kv_layout: Optional[str] = None,
-              seq_lens: Optional[torch.Tensor] = None, kernel: str = "auto") -> "ExactDecodePlan":
+              seq_lens: Optional[torch.Tensor] = None, kernel: str = "auto",
+              dynamic_schedule: Optional[bool] = None) -> "ExactDecodePlan":
         """Bind a plan.
 
         ``query`` and ``output`` may be pinned host tensors (the kernel then reads
@@ -60,7 +61,10 @@ class ExactDecodePlan:
         as in the reference.  ``num_splits`` asks for that many CTAs per
         (row, KV head); ``None`` sizes the grid to the GPU.  ``promoted_only``
         is accepted for compatibility and has no effect: every supported shape
-        is served.
+        is served.  ``dynamic_schedule=True`` lets the CTAs of a (row, KV head)
+        pair claim tiles from a device counter (a few percent faster when HBM
+        bound; results stay within tolerance but are no longer bit-identical
+        from launch to launch); ``None`` follows ``STREAMATTN_B200_SCHEDULE``.
         """
 
         del promoted_only
@@ -83,7 +87,7 @@ class ExactDecodePlan:
         num_ctas = 0 if num_splits is None else int(num_splits) * batch * kv_heads
         workspace = native.new_workspace(key_cache.device, batch, q_heads, kv_heads, dim, num_ctas)
         plan = native.exact_plan(query, key_cache, value_cache, output, workspace, kv_layout=layout,
-                                 seq_lens=seq_lens, num_ctas=num_ctas, kernel=kernel)
+                                 seq_lens=seq_lens, num_ctas=num_ctas, kernel=kernel, dynamic=dynamic_schedule)
         pairs = batch * kv_heads
         return cls(query=query, key_cache=key_cache, value_cache=value_cache, output=output,
                    workspace=workspace, num_splits=max(1, -(-plan.num_ctas // pairs)), kv_layout=layout,

@@ -8,6 +8,7 @@ CUDA stream handle of their device.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional, Sequence
 
@@ -31,6 +32,7 @@ SA_KERNEL_AUTO = 0
 SA_KERNEL_STREAM = 1
 SA_KERNEL_GENERIC = 2
 SA_KERNEL = {"auto": SA_KERNEL_AUTO, "stream": SA_KERNEL_STREAM, "generic": SA_KERNEL_GENERIC}
+SA_KERNEL_FLAG_DYNAMIC = 0x100
 SA_KERNEL_NAMES = {SA_KERNEL_STREAM: "sm100_tma_mma_stream", SA_KERNEL_GENERIC: "sm100_generic_simt"}
 SA_DEV_PIPELINE_TIMEOUT = 1
 SA_DEV_BAD_PAGE = 2
@@ -284,10 +286,28 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else int(t.data_ptr())
 
 
+def dynamic_default() -> bool:
+    """Whether plans use the dynamic tile schedule when the caller does not say.
+
+    ``STREAMATTN_B200_SCHEDULE=dynamic`` turns it on: a few percent faster on HBM-bound calls,
+    results within tolerance but no longer bit-identical from one launch to the next.
+    """
+
+    return os.environ.get("STREAMATTN_B200_SCHEDULE", "static").strip().lower() == "dynamic"
+
+
+def _kernel_code(kernel: str, dynamic: Optional[bool]) -> int:
+    if kernel not in SA_KERNEL:
+        raise ValueError(f"kernel must be one of {sorted(SA_KERNEL)}")
+    if dynamic is None:
+        dynamic = dynamic_default()
+    return SA_KERNEL[kernel] | (SA_KERNEL_FLAG_DYNAMIC if dynamic else 0)
+
+
 def exact_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
                workspace: torch.Tensor, *, kv_layout: str = "BNHD",
                seq_lens: Optional[torch.Tensor] = None, out_state: bool = False,
-               num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
+               num_ctas: int = 0, kernel: str = "auto", dynamic: Optional[bool] = None) -> NativePlan:
     device = require_cuda(key, value, workspace, seq_lens, host_io=(query, output))
     if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
         raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
@@ -303,7 +323,7 @@ def exact_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, outp
             _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(workspace), workspace.numel(),
             _ptr(seq_lens), lens_dtype, batch, q_heads, kv_heads, dim, kv_len,
             q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
-            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), SA_KERNEL[kernel],
+            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), _kernel_code(kernel, dynamic),
         )
     return NativePlan(handle, device, (query, key, value, output, workspace, seq_lens))
 
@@ -355,7 +375,8 @@ def exact_decode_static(query: torch.Tensor, key: torch.Tensor, value: torch.Ten
 def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.Tensor,
                page_table: torch.Tensor, seq_lens: torch.Tensor, output: torch.Tensor,
                workspace: torch.Tensor, *, layout: str, trace: Optional[torch.Tensor] = None,
-               out_state: bool = False, num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
+               out_state: bool = False, num_ctas: int = 0, kernel: str = "auto",
+               dynamic: Optional[bool] = None) -> NativePlan:
     device = require_cuda(key_pages, value_pages, page_table, seq_lens, workspace, trace, host_io=(query, output))
     layout = layout.upper()
     if layout not in SA_LAYOUT:
@@ -381,7 +402,7 @@ def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.
             _ptr(output), _ptr(workspace), workspace.numel(), _ptr(trace),
             batch, q_heads, kv_heads, dim, page_size, int(page_table.shape[1]), num_pages,
             SA_LAYOUT[layout], SA_DTYPE[query.dtype], SA_INDEX[page_table.dtype], SA_INDEX[seq_lens.dtype],
-            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), SA_KERNEL[kernel],
+            SA_OUT_STATE if out_state else SA_OUT_FINAL, int(num_ctas), _kernel_code(kernel, dynamic),
         )
     return NativePlan(handle, device,
                       (query, key_pages, value_pages, page_table, seq_lens, output, workspace, trace))

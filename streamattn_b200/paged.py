@@ -145,13 +145,15 @@ class PagedExactDecodePlan:
     @classmethod
     def build(cls, query: torch.Tensor, cache: PagedKVCache, *, output: Optional[torch.Tensor] = None,
               splits: Optional[int] = None, validate_metadata: bool = True, record_page_walk: bool = False,
-              kernel: str = "auto", **_compat: Any) -> "PagedExactDecodePlan":
+              kernel: str = "auto", dynamic_schedule: Optional[bool] = None,
+              **_compat: Any) -> "PagedExactDecodePlan":
         """Validate once and bind a plan.
 
         ``splits`` asks for that many CTAs per (row, KV head); ``None`` sizes the
         grid to the GPU.  ``record_page_walk`` adds an int32 ``trace`` tensor
         shaped like the page table in which every run records the physical page
-        it loaded per visited logical page.  Launch hints of the reference's
+        it loaded per visited logical page.  ``dynamic_schedule`` as in
+        ``ExactDecodePlan.build`` (faster, not bit-reproducible).  Launch hints of the reference's
         Triton path (``tokens_per_tile`` and friends) are accepted and ignored.
         """
 
@@ -171,7 +173,7 @@ class PagedExactDecodePlan:
         trace = torch.full_like(cache.page_table, -1, dtype=torch.int32) if record_page_walk else None
         plan = native.paged_plan(query, cache.key, cache.value, cache.page_table, cache.sequence_lengths,
                                  output, workspace, layout=cache.normalized_layout, trace=trace,
-                                 num_ctas=num_ctas, kernel=kernel)
+                                 num_ctas=num_ctas, kernel=kernel, dynamic=dynamic_schedule)
         pairs = batch * cache.kv_heads
         backend = PAGED_EXACT_SM100_BACKEND if plan.kernel == native.SA_KERNEL_STREAM else PAGED_EXACT_NATIVE_BACKEND
         return cls(query=query, cache=cache, output=output, splits=max(1, -(-plan.num_ctas // pairs)),

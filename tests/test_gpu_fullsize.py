@@ -71,7 +71,17 @@ def test_config2_exact_contiguous_b8_n65536(dev):
     assert torch.equal(plan.run(), out)                             # deterministic replay
     # BNHD view of the same values gives the same answer.
     kb, vb = k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous()
-    _close(sa.ExactDecodePlan.build(q, kb, vb, kv_layout="BNHD").run(), want)
+    bnhd = sa.ExactDecodePlan.build(q, kb, vb, kv_layout="BNHD")
+    first_bnhd = bnhd.run().clone()
+    _close(first_bnhd, want)
+    assert torch.equal(bnhd.run(), first_bnhd)                      # the round-robin schedule is static too
+    # Dynamic schedule (tiles claimed from a device counter): same answer within tolerance on
+    # every launch, counters left clean for the next one.
+    for layout, kk, vv in (("BHND", k, v), ("BNHD", kb, vb)):
+        dyn = sa.ExactDecodePlan.build(q, kk, vv, kv_layout=layout, dynamic_schedule=True)
+        for _ in range(3):
+            _close(dyn.run(), want)
+        assert dyn.device_status() == 0
     # Split-count invariance and linearity in V.
     _close(sa.ExactDecodePlan.build(q, k, v, num_splits=3).run(), want)
     v2 = (v.float() * 2).bfloat16()
@@ -117,6 +127,12 @@ def test_config3_paged_page16_ragged(dev):
     _close(out, torch_reference(q, kc, vc, lengths))
     # Bit-exact page walk: every active slot visited with its own physical page, -1 slots untouched.
     assert torch.equal(plan.trace.cpu(), table)
+    # Dynamic schedule: within tolerance on every launch, same page walk.
+    dyn = sa.PagedExactDecodePlan.build(q, cache, record_page_walk=True, dynamic_schedule=True)
+    for _ in range(3):
+        _close(dyn.run(), out.float())
+    assert dyn.device_status() == 0
+    assert torch.equal(dyn.trace.cpu(), table)
     # The same values through an int64 table and a forced split count.
     cache64 = sa.PagedKVCache(key=k, value=v, page_table=table.to(dev).long(), sequence_lengths=lengths.to(dev).long(),
                               layout="HND")

@@ -79,6 +79,22 @@ def test_exact_stream_kernel(dev, name, dtype, layout):
 
 
 @pytest.mark.parametrize("layout", ["BNHD", "BHND"])
+@pytest.mark.parametrize("name", STREAM_EXACT)
+def test_exact_stream_kernel_dynamic_schedule(dev, name, layout):
+    """SA_KERNEL_FLAG_DYNAMIC: tiles claimed from a device counter; within tolerance on every launch."""
+
+    case = cases.EXACT_CASES[name]
+    q, k, v = (t.to(torch.bfloat16) for t in cases.exact_inputs(case))
+    want = cpu_oracle.exact_decode(q, k, v)
+    plan, out, ws, _ = _exact_plan(dev, q, k, v, layout=layout, kernel="stream", dynamic=True)
+    for _ in range(3):
+        out.zero_()
+        plan.run()
+        assert native.workspace_status(ws) == 0
+        assert_close(out, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("layout", ["BNHD", "BHND"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", list(cases.EXACT_CASES))
 def test_exact_generic_kernel(dev, name, dtype, layout):
