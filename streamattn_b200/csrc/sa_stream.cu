@@ -13,6 +13,7 @@
 //
 // The same kernel serves contiguous caches, paged caches (page-table lookup per
 // fragment) and seed-only decode (a short list of cache blocks).
+#include <cstdlib>
 #include <mutex>
 
 #include "sa_stream.cuh"
@@ -314,6 +315,86 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_
     }
 }
 
+// Exact merge of the `nseg` split states of one (row, kv head) pair by all threads of the CTA
+// (items <= NTHREADS).  A work item is 4 columns of one head row; NTHREADS / items threads share
+// an item and each takes every (NTHREADS / items)-th state, requesting its o rows together with
+// their (m, l) in one batch, so the whole merge costs one round trip to L2.  The per-thread
+// results meet in shared memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l).
+// Out of line so that the rows in flight do not weigh on the streaming loop's registers.
+template <int D, int NTHREADS>
+__device__ __noinline__ void merge_pair_states(const float *first_slot, int64_t slot_stride, int nseg, int items,
+                                               float *sm, int tid)
+{
+    constexpr int PART_STRIDE = D + 4;
+    constexpr int BATCH = 8;
+    const int parts = NTHREADS / items;
+    const int part = tid / items;
+    const int item = tid - part * items;
+    const bool active = part < parts;
+    const int row = item / (D / 4);
+    const int d4 = (item - row * (D / 4)) * 4;
+    const float *src = first_slot + row * PART_STRIDE;
+    float big = -INFINITY, total_l = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int i0 = part; active && i0 < nseg; i0 += parts * BATCH) {  // one pass up to 8 * parts states
+        float4 o[BATCH];
+        float2 ml[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const int i = i0 + u * parts;
+            if (i < nseg) {
+                o[u] = __ldcg(reinterpret_cast<const float4 *>(src + i * slot_stride + d4));
+                ml[u] = __ldcg(reinterpret_cast<const float2 *>(src + i * slot_stride + D));
+            } else {
+                o[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                ml[u] = make_float2(-INFINITY, 0.0f);
+            }
+        }
+        float nb = big;
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) nb = fmaxf(nb, ml[u].x);
+        const float keep = exp2_diff(big, nb);
+        acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+        total_l *= keep;
+        big = nb;
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const float wgt = exp2_diff(ml[u].x, big);
+            acc.x += wgt * o[u].x;
+            acc.y += wgt * o[u].y;
+            acc.z += wgt * o[u].z;
+            acc.w += wgt * o[u].w;
+            total_l += wgt * ml[u].y;
+        }
+    }
+    if (active) {
+        float *mine = sm + (part * items + item) * 6;
+        *reinterpret_cast<float2 *>(mine) = make_float2(acc.x, acc.y);
+        *reinterpret_cast<float2 *>(mine + 2) = make_float2(acc.z, acc.w);
+        *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
+    }
+    __syncthreads();
+    if (part == 0 && parts > 1) {
+        for (int q = 1; q < parts; ++q) {
+            const float *other = sm + (q * items + item) * 6;
+            const float ob = other[4];
+            const float nb = fmaxf(big, ob);
+            const float keep = exp2_diff(big, nb), wgt = exp2_diff(ob, nb);
+            acc.x = acc.x * keep + wgt * other[0];
+            acc.y = acc.y * keep + wgt * other[1];
+            acc.z = acc.z * keep + wgt * other[2];
+            acc.w = acc.w * keep + wgt * other[3];
+            total_l = total_l * keep + wgt * other[5];
+            big = nb;
+        }
+        float *mine = sm + item * 6;
+        *reinterpret_cast<float2 *>(mine) = make_float2(acc.x, acc.y);
+        *reinterpret_cast<float2 *>(mine + 2) = make_float2(acc.z, acc.w);
+        *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
+    }
+    __syncthreads();
+}
+
 // One fragment (TMA box) of a tile as seen by the issuing lane.
 struct Frag {
     int x;              // global tile index, -1: no tile (warp-uniform)
@@ -383,6 +464,12 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Programmatic dependent launch: let the next kernel of the stream be scheduled as this
+    // grid's CTAs retire, and hold this grid here - before its first global-memory access -
+    // until everything launched earlier in the stream has completed and is visible.  Stream
+    // order is unchanged; only launch latency and the set-up above overlap the previous tail.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (ragged) {
         // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
         if (warp == 0) {
@@ -1033,6 +1120,15 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 // Last CTA to arrive on this pair: exact merge of its nseg split states.  All loads
                 // are issued before they are needed (the states sit in L2, ~1 us away).
                 const float *first_slot = p.partials + (static_cast<int64_t>(first_cta) + pair) * slot_stride;
+                if (items <= NTHREADS) {
+                    // The state areas are free again: the merged rows come back through them.
+                    merge_pair_states<D, NTHREADS>(first_slot, slot_stride, nseg, items, states, tid);
+                    if (tid < items) {
+                        const int row = tid / (D / 4);
+                        const float *r = states + tid * 6;
+                        store_result(row, (tid - row * (D / 4)) * 4, make_float4(r[0], r[1], r[2], r[3]), r[4], r[5]);
+                    }
+                } else {
                 constexpr int CAP = WARPS * STATE_FLOATS / 2;
                 float *sm_m = states;        // the state areas are free again: reuse them for (m, l)
                 float *sm_l = states + CAP;
@@ -1083,6 +1179,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     }
                     store_result(row, d4, acc, big, total_l);
                 }
+                }
                 if (tid == 0) {  // ready for the next launch: every CTA of the pair has arrived
                     p.counters[pair] = 0;
                     if (dyn_claims) p.pool[pair] = 0;
@@ -1131,8 +1228,19 @@ cudaError_t launch_instance(const CUtensorMap &mk, const CUtensorMap &mv, const 
             configured[dev] = smem;
         }
     }
-    kernel<<<ctas, WARPS * 32, smem, stream>>>(mk, mv, sp);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    // STREAMATTN_B200_NO_PDL=1 launches with plain stream serialization (for A/B timing).
+    static const int overlap_launch = std::getenv("STREAMATTN_B200_NO_PDL") ? 0 : 1;
+    attr[0].val.programmaticStreamSerializationAllowed = overlap_launch;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, mk, mv, sp);
 }
 
 template <typename T, int D>
