@@ -50,7 +50,7 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until a capture exists for the workload).
-NCU_TRAFFIC_BYTES = {"exact_c2": 272.0e6, "paged_c3": 170.8e6}
+NCU_TRAFFIC_BYTES = {"exact_c2": 272.3e6, "paged_c3": 170.9e6}
 
 
 def measured_hbm_peak():

@@ -393,3 +393,35 @@ def test_one_shot_c_abi_calls(dev):
                              native.SA_DTYPE[torch.bfloat16], native.SA_OUT_FINAL, 0, native.SA_KERNEL_AUTO, stream)
     assert rc == native.SA_ERR_INVALID
     torch.cuda.synchronize()
+
+
+def test_plans_replay_inside_a_cuda_graph(dev):
+    """A decode step captured into a CUDA graph (three launches back to back, the way a decode
+    loop replays them) gives the bits of the eager run; the kernels are launched with
+    programmatic stream serialization, which must survive capture."""
+
+    g = torch.Generator().manual_seed(5)
+    batch, q_heads, kv_heads, dim, kv_len = 4, 16, 2, 64, 4096
+    q = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16().to(dev)
+    k = torch.randn(batch, kv_heads, kv_len, dim, generator=g).bfloat16().to(dev)
+    v = torch.randn(batch, kv_heads, kv_len, dim, generator=g).bfloat16().to(dev)
+    out = torch.empty_like(q)
+    ws = native.new_workspace(dev, batch, q_heads, kv_heads, dim)
+    plan = native.exact_plan(q, k, v, out, ws, kv_layout="BHND", kernel="stream")
+    plan.run()
+    torch.cuda.synchronize()
+    eager = out.clone()
+    side = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        plan.run()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):
+                plan.run()
+    for _ in range(2):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    assert native.workspace_status(ws) == 0
