@@ -453,12 +453,16 @@ def main() -> None:
         barrier()
 
     single_gpu_us = None
+    cp_max_abs = None
     if workload == "cp_c5" and world > 1 and rank == 0:
         # One-GPU time of the same 1M-token row, measured in this run on rank 0 (not in the timed region).
         full = build_cp_c5_single(device)
         for _ in range(3):
             full()
         single_gpu_us = time_region(full, 10, device) / 10 * 1e6
+        # Same values on one GPU: the sharded result must agree within the bf16 output tolerance.
+        cp_max_abs = float((full().float() - out_dev.float()).abs().max())
+        assert cp_max_abs <= 2e-2, f"context-parallel result differs from the one-GPU result by {cp_max_abs}"
     if distributed:
         barrier()
 
@@ -487,6 +491,7 @@ def main() -> None:
             line["cp_local_kernel_us"] = local_kernel_us
         if single_gpu_us is not None:
             line["cp_single_gpu_us"] = single_gpu_us
+            line["cp_max_abs_vs_1gpu"] = cp_max_abs
             line["cp_speedup_vs_1gpu"] = single_gpu_us / (step_s * 1e6)
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_sample(workload)

@@ -205,19 +205,18 @@ template <> struct Mma<__half> {
     }
 };
 
-// Copy the tagged words of one pair's state rows (`words` contiguous 8-byte words at word offset
-// `start` of every rank's buffer) from this rank's own buffer to all peers.  Consecutive lanes
+// Send the tagged words of one pair's state rows - staged in shared memory by the finishing
+// CTA - to word offset `start` of every rank's buffer (own rank included).  Consecutive lanes
 // move consecutive 16-byte pieces, so one warp store covers 512 contiguous bytes: small scattered
 // stores are what NVLink handles worst.  Each 8-byte half carries its own step tag, so the copy
 // needs no ordering or atomicity beyond that of an aligned 8-byte access.
 template <int NTHREADS>
-__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, size_t start, int words, int tid)
+__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, const uint2 *stage, size_t start, int words, int tid)
 {
-    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint2 *>(cp.bases[cp.rank]) + start);
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage);
     for (int i = tid; i < words / 2; i += NTHREADS) {  // `start` and `words` are even: 16-byte pieces
-        const uint4 v = __ldcg(src + i);
+        const uint4 v = src[i];
         for (int r = 0; r < cp.world; ++r) {
-            if (r == cp.rank) continue;
             uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[r]) + start) + i;
             asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y),
                          "r"(v.z), "r"(v.w)
@@ -227,91 +226,106 @@ __device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, size_t start, i
 }
 
 // Context-parallel finish of one (row, kv head) pair, run by the CTA that completed the pair on
-// this rank after it stored the pair's state rows to every rank: wait (bounded) for the same rows
+// this rank after it sent the pair's state rows to every rank: wait (bounded) for the same rows
 // from all ranks - each 8-byte word carries the step number, so the data is its own flag - then
-// merge them exactly and write the final output rows.  Kept out of line so its registers do not
-// weigh on the streaming loop.
+// merge them exactly and write the final output rows.  A work item is 4 columns of one head row;
+// NTHREADS / items threads share an item and each polls every (NTHREADS / items)-th rank, four
+// ranks' (o[4], m, l) words at a time, so the wait costs one round of loads after the data
+// landed; the threads of an item meet through shared memory (`sm`, 6 floats per thread).  Kept
+// out of line so its registers do not weigh on the streaming loop.
 template <typename T, int D, int NTHREADS>
 __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_t total_rows, int64_t out_row0,
-                                            int items, int tid)
+                                            int items, float *sm, int tid)
 {
     constexpr int STATE_STRIDE = D + 2;
+    constexpr int RB = 4;  // ranks polled together by one thread
     const uint2 *gather = reinterpret_cast<const uint2 *>(cp.bases[cp.rank]) + (cp.step & 1u) * cp.gather_floats_per_parity;
     const size_t rank_stride = total_rows * STATE_STRIDE;
-    for (int item = tid; item < items; item += NTHREADS) {
+    const int parts = items <= NTHREADS ? NTHREADS / items : 1;
+    const unsigned long long t0 = global_timer_ns();
+    for (int first = 0; first < items; first += NTHREADS) {  // a single pass unless items > NTHREADS
+        const int part = parts > 1 ? tid / items : 0;
+        const int item = parts > 1 ? tid - part * items : first + tid;
+        const bool active = part < parts && item < items;
         const int row = item / (D / 4);
         const int d4 = (item - row * (D / 4)) * 4;
-        const uint2 *row0 = gather + (out_row0 + row) * STATE_STRIDE;
-        const unsigned long long t0 = global_timer_ns();
-        // (m, l) of every rank first: they fix the weights.
-        float m[kCpFuseWorld], l[kCpFuseWorld];
-        bool waiting = true;
-        while (waiting) {
-            waiting = false;
-#pragma unroll
-            for (int r = 0; r < kCpFuseWorld; ++r) {
-                if (r < cp.world) {
-                    const uint2 wm = cp_load(row0 + r * rank_stride + D);
-                    const uint2 wl = cp_load(row0 + r * rank_stride + D + 1);
-                    m[r] = __uint_as_float(wm.x);
-                    l[r] = __uint_as_float(wl.x);
-                    waiting |= wm.y != cp.step || wl.y != cp.step;
-                } else {
-                    m[r] = -INFINITY;
-                    l[r] = 0.0f;
-                }
-            }
-            if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
-                atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
-                break;
-            }
-        }
-        float big = -INFINITY;
-#pragma unroll
-        for (int r = 0; r < kCpFuseWorld; ++r)
-            if (l[r] > 0.0f) big = fmaxf(big, m[r]);
+        float big = -INFINITY, total_l = 0.0f;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        float total_l = 0.0f;
-        // Then the four columns of this item, four ranks at a time.
+        if (active) {
+            const uint2 *row0 = gather + (out_row0 + row) * STATE_STRIDE;
+            for (int r0 = part; r0 < cp.world; r0 += parts * RB) {
+                uint2 w[RB][6];
+                bool waiting = true;
+                while (waiting) {
+                    waiting = false;
 #pragma unroll
-        for (int r0 = 0; r0 < kCpFuseWorld; r0 += 4) {
-            if (r0 >= cp.world) break;
-            uint2 w[4][4];
-            waiting = true;
-            while (waiting) {
-                waiting = false;
+                    for (int u = 0; u < RB; ++u) {
+                        const int r = r0 + u * parts;
+                        if (r < cp.world) {
+                            const uint2 *st = row0 + r * rank_stride;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (r0 + i < cp.world) {
-                        const uint2 *st = row0 + (r0 + i) * rank_stride + d4;
+                            for (int j = 0; j < 4; ++j) w[u][j] = cp_load(st + d4 + j);
+                            w[u][4] = cp_load(st + D);
+                            w[u][5] = cp_load(st + D + 1);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            w[i][j] = cp_load(st + j);
-                            waiting |= w[i][j].y != cp.step;
+                            for (int j = 0; j < 6; ++j) waiting |= w[u][j].y != cp.step;
                         }
                     }
+                    if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
+                        atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
+                        break;
+                    }
                 }
-                if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
-                    atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
-                    break;
-                }
-            }
+                float nb = big;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (r0 + i < cp.world) {
-                    const float wgt = l[r0 + i] > 0.0f ? exp2_diff(m[r0 + i], big) : 0.0f;
-                    acc.x += wgt * __uint_as_float(w[i][0].x);
-                    acc.y += wgt * __uint_as_float(w[i][1].x);
-                    acc.z += wgt * __uint_as_float(w[i][2].x);
-                    acc.w += wgt * __uint_as_float(w[i][3].x);
-                    total_l += wgt * l[r0 + i];
+                for (int u = 0; u < RB; ++u)
+                    if (r0 + u * parts < cp.world) nb = fmaxf(nb, __uint_as_float(w[u][4].x));
+                const float keep = exp2_diff(big, nb);
+                acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+                total_l *= keep;
+                big = nb;
+#pragma unroll
+                for (int u = 0; u < RB; ++u) {
+                    if (r0 + u * parts < cp.world) {
+                        const float wgt = exp2_diff(__uint_as_float(w[u][4].x), big);
+                        acc.x += wgt * __uint_as_float(w[u][0].x);
+                        acc.y += wgt * __uint_as_float(w[u][1].x);
+                        acc.z += wgt * __uint_as_float(w[u][2].x);
+                        acc.w += wgt * __uint_as_float(w[u][3].x);
+                        total_l += wgt * __uint_as_float(w[u][5].x);
+                    }
                 }
             }
         }
-        const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
-        T *dst = static_cast<T *>(cp.final_out) + (out_row0 + row) * D + d4;
-        *reinterpret_cast<uint2 *>(dst) =
-            make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
+        if (parts > 1) {
+            if (active && part > 0) {
+                float *mine = sm + ((part - 1) * items + item) * 6;
+                *reinterpret_cast<float2 *>(mine) = make_float2(acc.x, acc.y);
+                *reinterpret_cast<float2 *>(mine + 2) = make_float2(acc.z, acc.w);
+                *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
+            }
+            __syncthreads();
+            if (active && part == 0) {
+                for (int q = 1; q < parts; ++q) {
+                    const float *other = sm + ((q - 1) * items + item) * 6;
+                    const float ob = other[4];
+                    const float nb = fmaxf(big, ob);
+                    const float keep = exp2_diff(big, nb), wgt = exp2_diff(ob, nb);
+                    acc.x = acc.x * keep + wgt * other[0];
+                    acc.y = acc.y * keep + wgt * other[1];
+                    acc.z = acc.z * keep + wgt * other[2];
+                    acc.w = acc.w * keep + wgt * other[3];
+                    total_l = total_l * keep + wgt * other[5];
+                    big = nb;
+                }
+            }
+        }
+        if (active && part == 0) {
+            const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
+            T *dst = static_cast<T *>(cp.final_out) + (out_row0 + row) * D + d4;
+            *reinterpret_cast<uint2 *>(dst) =
+                make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
+        }
     }
 }
 
@@ -428,7 +442,8 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + WARPS * STAGES * kStageBytes);
     float *states = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + BAR_BYTES);
-    int *prefix = reinterpret_cast<int *>(states + WARPS * STATE_FLOATS);  // ragged rows: tiles before row b
+    uint2 *cp_stage = reinterpret_cast<uint2 *>(states + WARPS * STATE_FLOATS);  // context-parallel: rows to send
+    int *prefix = reinterpret_cast<int *>(cp_stage + STATE_FLOATS);            // ragged rows: tiles before row b
     int *vlens = prefix + p.batch + 1;                                      // ragged rows: length of row b
     __shared__ int s_last;
 
@@ -1044,22 +1059,19 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 *reinterpret_cast<uint2 *>(dst) =
                     make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
             } else if (p.cp.world > 0) {
-                // Context-parallel: this rank's state row goes straight into every rank's gather
-                // buffer (plain peer stores over NVLink, own copy included).  Every value travels
-                // as an 8-byte word {value, step}: the word is written atomically, so a reader that
-                // sees the step number also sees the value - no fence or separate flag round trip.
-                const size_t off = (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
-                                   (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0 + row) * STATE_STRIDE;
-                // Here only this rank's own buffer is written; cp_broadcast_pair() then copies the
-                // pair's rows to the peers with wide, lane-contiguous stores.
-                uint2 *dst = reinterpret_cast<uint2 *>(p.cp.bases[p.cp.rank]) + off;
-                cp_store(dst + d4, acc.x, p.cp.step);
-                cp_store(dst + d4 + 1, acc.y, p.cp.step);
-                cp_store(dst + d4 + 2, acc.z, p.cp.step);
-                cp_store(dst + d4 + 3, acc.w, p.cp.step);
+                // Context-parallel: the pair's state rows are staged in shared memory as 8-byte
+                // words {value, step}; cp_broadcast_pair() then sends them to every rank's gather
+                // buffer with wide, lane-contiguous stores.  A word is written atomically, so a
+                // reader that sees the step number also sees the value - no fence or separate
+                // flag round trip.
+                uint2 *dst = cp_stage + row * STATE_STRIDE;
+                dst[d4] = make_uint2(__float_as_uint(acc.x), p.cp.step);
+                dst[d4 + 1] = make_uint2(__float_as_uint(acc.y), p.cp.step);
+                dst[d4 + 2] = make_uint2(__float_as_uint(acc.z), p.cp.step);
+                dst[d4 + 3] = make_uint2(__float_as_uint(acc.w), p.cp.step);
                 if (d4 == 0) {
-                    cp_store(dst + D, big, p.cp.step);
-                    cp_store(dst + D + 1, total_l, p.cp.step);
+                    dst[D] = make_uint2(__float_as_uint(big), p.cp.step);
+                    dst[D + 1] = make_uint2(__float_as_uint(total_l), p.cp.step);
                 }
             } else {
                 float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
@@ -1187,15 +1199,15 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         }
         if (p.cp.world > 0 && (nseg == 1 || s_last)) {
-            __syncthreads();  // the pair's rows are complete in this rank's own buffer
+            __syncthreads();  // the pair's rows are complete in the staging area; the state areas are free
             cp_broadcast_pair<NTHREADS>(
-                p.cp,
+                p.cp, cp_stage,
                 (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
                     (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0) * STATE_STRIDE,
                 group * STATE_STRIDE, tid);
+            cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, static_cast<size_t>(p.batch) * p.q_heads, out_row0, items,
+                                           states, tid);
         }
-        if (p.cp.world > 0 && (nseg == 1 || s_last))
-            cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, static_cast<size_t>(p.batch) * p.q_heads, out_row0, items, tid);
         __syncthreads();  // the state areas and s_last are reused by the next segment
         SA_STAMP(6);
         cur = seg_end;
@@ -1275,7 +1287,8 @@ int stream_stages(int head_dim, bool rows16)
 size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch)
 {
     const size_t bars = (static_cast<size_t>(kStreamWarps) * stages * 8 + 15) / 16 * 16;
-    const size_t states = static_cast<size_t>(kStreamWarps) * (rows16 ? 16 : 8) * (head_dim + 2) * 4;
+    // Per-warp (o, m, l) areas plus the context-parallel staging rows (8-byte words).
+    const size_t states = (static_cast<size_t>(kStreamWarps) + 2) * (rows16 ? 16 : 8) * (head_dim + 2) * 4;
     return 1024 + static_cast<size_t>(kStreamWarps) * stages * kStageBytes + bars + states +
            (2 * static_cast<size_t>(batch) + 1) * 4 + 16;
 }
