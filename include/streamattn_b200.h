@@ -305,6 +305,50 @@ SA_API int sa_plan_num_ctas(const sa_plan_t *plan);
 SA_API int sa_plan_launches(const sa_plan_t *plan);
 SA_API void sa_plan_destroy(sa_plan_t *plan);
 
+/* ---- KV-cache update: the step before each decode call ------------------------------------
+ * Writes the current token's K/V row of every (row, KV head) into the cache at the row's
+ * position, optionally after the rotary embedding, and optionally rotates the query as well:
+ *     x' = x * cos + rotate_half(x) * sin,   rotate_half(x) = concat(-x[D/2:], x[:D/2])
+ * evaluated in the cache dtype with every product and the sum rounded to that dtype, i.e. the
+ * bits of the same expression on torch tensors.  Replaces the reference's
+ * `_apply_qwen_rope` + `copy_` pair (benchmarks/profile_seed_only_fused_rope_parity.py:24-30,
+ * 97-102), its append kernel (benchmarks/profile_kv_cache_update_floor.py:46-75) and the
+ * RoPE + append prologue of its fused seed kernel (kernels/gate0_seed_only_triton.py:731-770).
+ *
+ *   k_new, v_new   [batch, kv_heads, D] rows, strides new_stride_b / new_stride_h (elements)
+ *   positions      device int32/int64: one entry (all rows share it, like the reference's
+ *                  cache_position) or one per row; the token index written
+ *   lens_out       optional device array [batch] (same integer type): receives position + 1;
+ *                  may be the per-row `positions` array itself (in-place length advance)
+ *   cos, sin       optional [batch or 1, D] in the cache dtype (rope_stride_b = 0: shared row);
+ *                  NULL = plain append
+ *   q_in / q_out   optional [batch, q_heads, D] rows (own strides): rotated query; must not alias
+ *   status         optional device int32: SA_DEV_BAD_POSITION / SA_DEV_BAD_PAGE are OR-ed in when a
+ *                  row's position or page id is out of range (that row is skipped, never written)
+ */
+#define SA_DEV_BAD_POSITION 4
+SA_API int sa_append_kv(const void *k_new, const void *v_new, void *k_cache, void *v_cache,
+                        const void *positions, int pos_dtype, int num_positions, void *lens_out,
+                        const void *cos, const void *sin, int64_t rope_stride_b,
+                        const void *q_in, void *q_out, int q_heads,
+                        int64_t q_in_stride_b, int64_t q_in_stride_h, int64_t q_out_stride_b, int64_t q_out_stride_h,
+                        int batch, int kv_heads, int head_dim, int64_t kv_len,
+                        int64_t new_stride_b, int64_t new_stride_h,
+                        int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                        int dtype, int *status, sa_stream_t stream);
+/* Same for a paged cache: the row goes to slot position % page_size of page
+ * page_table[b][position / page_size], which the caller's allocator must have assigned. */
+SA_API int sa_paged_append_kv(const void *k_new, const void *v_new, void *k_pages, void *v_pages,
+                              const void *page_table, int table_dtype,
+                              const void *positions, int pos_dtype, int num_positions, void *lens_out,
+                              const void *cos, const void *sin, int64_t rope_stride_b,
+                              const void *q_in, void *q_out, int q_heads,
+                              int64_t q_in_stride_b, int64_t q_in_stride_h, int64_t q_out_stride_b,
+                              int64_t q_out_stride_h,
+                              int batch, int kv_heads, int head_dim, int page_size, int max_pages,
+                              int64_t num_pages, int layout, int64_t new_stride_b, int64_t new_stride_h,
+                              int dtype, int *status, sa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -125,3 +125,67 @@ def seed_decode(
     probs = torch.softmax(scores, dim=-1)
     out = torch.einsum("bhs,bshd->bhd", probs, v_q)
     return out[:, None].to(query.dtype)
+
+
+def qwen_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x`` [B, H, 1, D] with ``cos``/``sin`` [B, 1, D], in the tensors' dtype.
+
+    Follows ``benchmarks/profile_seed_only_fused_rope_parity.py:24-30`` (``_rotate_half`` /
+    ``_apply_qwen_rope``): ``x * cos + concat(-x[D/2:], x[:D/2]) * sin``; every product and the sum
+    are rounded to the dtype, as torch does for half-precision tensors.
+    """
+
+    half = x.shape[-1] // 2
+    rotated = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return (x * cos.unsqueeze(1)) + (rotated * sin.unsqueeze(1))
+
+
+def rope_append(q_raw, k_raw, v_raw, cos, sin, key_cache, value_cache, positions):
+    """The reference's safe path for one decode step's cache update (same file, lines 92-102).
+
+    q_raw [B,Hq,1,D], k_raw/v_raw [B,Hkv,1,D], cos/sin [B or 1,1,D] (None: no rotation), caches
+    [B,Hkv,N,D] (updated in place), ``positions`` one int per row.  Returns the rotated query.
+    """
+
+    batch = k_raw.shape[0]
+    if cos is not None:
+        cos_b = cos.expand(batch, -1, -1)
+        sin_b = sin.expand(batch, -1, -1)
+        q_rot = qwen_rope(q_raw, cos_b, sin_b) if q_raw is not None else None
+        k_rot = qwen_rope(k_raw, cos_b, sin_b)
+    else:
+        q_rot, k_rot = q_raw, k_raw
+    for b, pos in enumerate(positions):
+        key_cache[b, :, pos : pos + 1, :].copy_(k_rot[b])
+        value_cache[b, :, pos : pos + 1, :].copy_(v_raw[b])
+    return q_rot
+
+
+def paged_rope_append(q_raw, k_raw, v_raw, cos, sin, key_pages, value_pages, page_table, positions, *, layout="NHD"):
+    """Same update for a paged cache: row b goes to slot ``pos % page`` of ``page_table[b][pos // page]``.
+
+    The reference has no paged writer; the addressing is that of its paged reader
+    (``stream_attention/paged.py:217-255``).  Pages [P,page,Hkv,D] (NHD) or [P,Hkv,page,D] (HND),
+    updated in place.
+    """
+
+    layout = layout.upper()
+    page_size = key_pages.shape[1] if layout == "NHD" else key_pages.shape[2]
+    batch = k_raw.shape[0]
+    if cos is not None:
+        cos_b = cos.expand(batch, -1, -1)
+        sin_b = sin.expand(batch, -1, -1)
+        q_rot = qwen_rope(q_raw, cos_b, sin_b) if q_raw is not None else None
+        k_rot = qwen_rope(k_raw, cos_b, sin_b)
+    else:
+        q_rot, k_rot = q_raw, k_raw
+    for b, pos in enumerate(positions):
+        page = int(page_table[b, pos // page_size])
+        slot = pos % page_size
+        if layout == "NHD":
+            key_pages[page, slot] = k_rot[b, :, 0, :]
+            value_pages[page, slot] = v_raw[b, :, 0, :]
+        else:
+            key_pages[page, :, slot] = k_rot[b, :, 0, :]
+            value_pages[page, :, slot] = v_raw[b, :, 0, :]
+    return q_rot

@@ -9,6 +9,7 @@
 #include <new>
 #include <vector>
 
+#include "sa_append.cuh"
 #include "sa_stream.cuh"
 
 namespace sa {
@@ -395,6 +396,56 @@ int fill_seed(sa_plan *plan, const void *q, const void *k, const void *v, void *
     p.seq.blocks_vlen = vlen;
     p.num_ctas = num_ctas;
     return finish_plan(plan, workspace, workspace_bytes, vlen, kernel_choice);
+}
+
+}  // namespace
+}  // namespace sa
+
+using namespace sa;
+
+namespace sa {
+namespace {
+
+// Checks shared by the two KV-append entry points; fills the parts of `a` that do not depend
+// on the cache kind.
+int fill_append(AppendParams *a, const void *k_new, const void *v_new, void *k_cache, void *v_cache,
+                const void *positions, int pos_dtype, int num_positions, void *lens_out, const void *cos,
+                const void *sin, int64_t rope_stride_b, const void *q_in, void *q_out, int q_heads,
+                int64_t q_in_stride_b, int64_t q_in_stride_h, int64_t q_out_stride_b, int64_t q_out_stride_h,
+                int batch, int kv_heads, int head_dim, int64_t new_stride_b, int64_t new_stride_h, int dtype,
+                int *status)
+{
+    if (!k_new || !v_new || !k_cache || !v_cache || !positions)
+        return fail(SA_ERR_INVALID, "null tensor pointer");
+    if (batch <= 0 || kv_heads <= 0) return fail(SA_ERR_INVALID, "batch/heads must be positive");
+    if (head_dim <= 0 || head_dim > 256) return fail(SA_ERR_INVALID, "head_dim must be in [1, 256]");
+    if (dtype < SA_DTYPE_BF16 || dtype > SA_DTYPE_F32) return fail(SA_ERR_INVALID, "unknown dtype");
+    if (pos_dtype != SA_INDEX_I32 && pos_dtype != SA_INDEX_I64) return fail(SA_ERR_INVALID, "positions must be int32 or int64");
+    if (num_positions != 1 && num_positions != batch)
+        return fail(SA_ERR_INVALID, "positions must hold one entry or one per batch row");
+    if (lens_out == positions && num_positions == 1 && batch > 1)
+        return fail(SA_ERR_INVALID, "lens_out may alias positions only when there is one position per row");
+    if ((cos == nullptr) != (sin == nullptr)) return fail(SA_ERR_INVALID, "cos and sin must be given together");
+    if (cos != nullptr && head_dim % 2) return fail(SA_ERR_INVALID, "rotary embedding needs an even head_dim");
+    if ((q_in == nullptr) != (q_out == nullptr)) return fail(SA_ERR_INVALID, "q_in and q_out must be given together");
+    if (q_in != nullptr && (q_heads <= 0 || q_heads % kv_heads))
+        return fail(SA_ERR_INVALID, "query heads must be a positive multiple of KV heads");
+    if (q_in != nullptr && q_in == q_out) return fail(SA_ERR_INVALID, "q_out must not alias q_in");
+    std::memset(a, 0, sizeof(*a));
+    a->k_new = k_new; a->v_new = v_new;
+    a->new_sb = new_stride_b; a->new_sh = new_stride_h;
+    a->k_cache = k_cache; a->v_cache = v_cache;
+    a->positions = positions;
+    a->pos_i64 = pos_dtype == SA_INDEX_I64;
+    a->pos_shared = num_positions == 1;
+    a->lens_out = lens_out;
+    a->cos = cos; a->sin = sin; a->rope_sb = rope_stride_b;
+    a->q_in = q_in; a->q_out = q_out; a->q_heads = q_heads;
+    a->qi_sb = q_in_stride_b; a->qi_sh = q_in_stride_h; a->qo_sb = q_out_stride_b; a->qo_sh = q_out_stride_h;
+    a->batch = batch; a->kv_heads = kv_heads; a->head_dim = head_dim;
+    a->dtype = dtype;
+    a->status = status;
+    return SA_OK;
 }
 
 }  // namespace
@@ -828,5 +879,68 @@ int sa_plan_launches(const sa_plan_t *plan)
 }
 
 void sa_plan_destroy(sa_plan_t *plan) { delete plan; }
+
+int sa_append_kv(const void *k_new, const void *v_new, void *k_cache, void *v_cache, const void *positions,
+                 int pos_dtype, int num_positions, void *lens_out, const void *cos, const void *sin,
+                 int64_t rope_stride_b, const void *q_in, void *q_out, int q_heads, int64_t q_in_stride_b,
+                 int64_t q_in_stride_h, int64_t q_out_stride_b, int64_t q_out_stride_h, int batch, int kv_heads,
+                 int head_dim, int64_t kv_len, int64_t new_stride_b, int64_t new_stride_h, int64_t kv_stride_b,
+                 int64_t kv_stride_n, int64_t kv_stride_h, int dtype, int *status, sa_stream_t stream)
+{
+    AppendParams a;
+    const int rc = fill_append(&a, k_new, v_new, k_cache, v_cache, positions, pos_dtype, num_positions, lens_out, cos,
+                               sin, rope_stride_b, q_in, q_out, q_heads, q_in_stride_b, q_in_stride_h,
+                               q_out_stride_b, q_out_stride_h, batch, kv_heads, head_dim, new_stride_b,
+                               new_stride_h, dtype, status);
+    if (rc) return rc;
+    if (kv_len <= 0) return fail(SA_ERR_INVALID, "kv_len must be positive");
+    if (kv_stride_n <= 0 || kv_stride_h < 0 || kv_stride_b < 0) return fail(SA_ERR_INVALID, "non-positive KV stride");
+    a.paged = 0;
+    a.kv_sb = kv_stride_b; a.kv_sn = kv_stride_n; a.kv_sh = kv_stride_h;
+    a.capacity = kv_len;
+    const cudaError_t err = launch_append(a, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "kernel launch failed");
+    return SA_OK;
+}
+
+int sa_paged_append_kv(const void *k_new, const void *v_new, void *k_pages, void *v_pages, const void *page_table,
+                       int table_dtype, const void *positions, int pos_dtype, int num_positions, void *lens_out,
+                       const void *cos, const void *sin, int64_t rope_stride_b, const void *q_in, void *q_out,
+                       int q_heads, int64_t q_in_stride_b, int64_t q_in_stride_h, int64_t q_out_stride_b,
+                       int64_t q_out_stride_h, int batch, int kv_heads, int head_dim, int page_size, int max_pages,
+                       int64_t num_pages, int layout, int64_t new_stride_b, int64_t new_stride_h, int dtype,
+                       int *status, sa_stream_t stream)
+{
+    AppendParams a;
+    const int rc = fill_append(&a, k_new, v_new, k_pages, v_pages, positions, pos_dtype, num_positions, lens_out, cos,
+                               sin, rope_stride_b, q_in, q_out, q_heads, q_in_stride_b, q_in_stride_h,
+                               q_out_stride_b, q_out_stride_h, batch, kv_heads, head_dim, new_stride_b,
+                               new_stride_h, dtype, status);
+    if (rc) return rc;
+    if (!page_table) return fail(SA_ERR_INVALID, "page_table is required");
+    if (table_dtype != SA_INDEX_I32 && table_dtype != SA_INDEX_I64)
+        return fail(SA_ERR_INVALID, "page_table must be int32 or int64");
+    if (page_size <= 0 || max_pages <= 0 || num_pages <= 0)
+        return fail(SA_ERR_INVALID, "paged cache dimensions must be positive");
+    if (layout != SA_LAYOUT_NHD && layout != SA_LAYOUT_HND) return fail(SA_ERR_INVALID, "paged KV layout must be NHD or HND");
+    a.paged = 1;
+    a.page_table = page_table;
+    a.table_i64 = table_dtype == SA_INDEX_I64;
+    a.max_pages = max_pages;
+    a.page_size = page_size;
+    a.num_pages = num_pages;
+    a.capacity = static_cast<int64_t>(max_pages) * page_size;
+    a.pg_sp = static_cast<int64_t>(page_size) * kv_heads * head_dim;
+    if (layout == SA_LAYOUT_NHD) {
+        a.pg_st = static_cast<int64_t>(kv_heads) * head_dim;
+        a.pg_sh = head_dim;
+    } else {
+        a.pg_sh = static_cast<int64_t>(page_size) * head_dim;
+        a.pg_st = head_dim;
+    }
+    const cudaError_t err = launch_append(a, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "kernel launch failed");
+    return SA_OK;
+}
 
 }  // extern "C"

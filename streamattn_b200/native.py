@@ -36,6 +36,7 @@ SA_KERNEL_FLAG_DYNAMIC = 0x100
 SA_KERNEL_NAMES = {SA_KERNEL_STREAM: "sm100_tma_mma_stream", SA_KERNEL_GENERIC: "sm100_generic_simt"}
 SA_DEV_PIPELINE_TIMEOUT = 1
 SA_DEV_BAD_PAGE = 2
+SA_DEV_BAD_POSITION = 4
 SA_MAX_SEED_BLOCKS = 256
 
 _vp = ctypes.c_void_p
@@ -81,6 +82,14 @@ _SIGNATURES = {
     "sa_plan_num_ctas": ([_vp], _i),
     "sa_plan_launches": ([_vp], _i),
     "sa_plan_destroy": ([_vp], None),
+    # k_new v_new k_cache v_cache | positions pos_dtype num_positions lens_out | cos sin rope_stride_b |
+    # q_in q_out q_heads 4 q strides | batch kv_heads head_dim kv_len | 2 new strides | 3 kv strides | dtype status stream
+    "sa_append_kv": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i64, _i64, _i64, _i64,
+                      _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _vp, _vp], _i),
+    # ... k_pages v_pages page_table table_dtype | positions ... | batch kv_heads head_dim page_size max_pages
+    # num_pages layout | 2 new strides | dtype status stream
+    "sa_paged_append_kv": ([_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i64, _i64,
+                            _i64, _i64, _i, _i, _i, _i, _i, _i64, _i, _i64, _i64, _i, _vp, _vp], _i),
 }
 
 _LOCK = threading.Lock()

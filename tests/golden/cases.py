@@ -188,3 +188,48 @@ def tensor_checksum(t: torch.Tensor) -> float:
     flat = t.detach().to(torch.float64).reshape(-1)
     weights = torch.arange(1, flat.numel() + 1, dtype=torch.float64) % 251 + 1.0
     return float((flat * weights).sum())
+
+
+# ---- KV-cache update (rotary embedding + append) --------------------------------------------
+
+@dataclass(frozen=True)
+class RopeAppendCase:
+    batch: int
+    q_heads: int
+    kv_heads: int
+    dim: int
+    max_seq: int
+    positions: Tuple[int, ...]   # one entry (shared) or one per row
+    shared_cos: bool
+    dtype: str                   # "bf16" | "fp16" | "fp32"
+    seed: int
+
+
+ROPE_APPEND_CASES: Dict[str, RopeAppendCase] = {
+    "qwen_bf16_shared_pos": RopeAppendCase(4, 16, 2, 128, 96, (37,), False, "bf16", 11),
+    "qwen_fp16_shared_cos": RopeAppendCase(2, 8, 2, 64, 64, (63,), True, "fp16", 12),
+    "rows_bf16_d64": RopeAppendCase(3, 8, 4, 64, 80, (0, 41, 79), False, "bf16", 13),
+    "rows_fp32_d32": RopeAppendCase(2, 4, 4, 32, 40, (5, 17), True, "fp32", 14),
+}
+
+ROPE_DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+def rope_append_inputs(case: RopeAppendCase):
+    """(q_raw [B,Hq,1,D], k_raw, v_raw [B,Hkv,1,D], cos, sin [B or 1,1,D], k_cache, v_cache [B,Hkv,N,D]).
+
+    Same recipe as the reference's parity script (scaled randn, angles ~ N(0,1) duplicated over
+    the two halves), generated on the CPU in float32 and cast to the case's dtype.
+    """
+
+    g = _gen(case.seed)
+    dtype = ROPE_DTYPES[case.dtype]
+    scale = 1.0 / (case.dim ** 0.5)
+    q_raw = (torch.randn(case.batch, case.q_heads, 1, case.dim, generator=g) * scale).to(dtype)
+    k_raw = (torch.randn(case.batch, case.kv_heads, 1, case.dim, generator=g) * scale).to(dtype)
+    v_raw = torch.randn(case.batch, case.kv_heads, 1, case.dim, generator=g).to(dtype)
+    k_cache = (torch.randn(case.batch, case.kv_heads, case.max_seq, case.dim, generator=g) * scale).to(dtype)
+    v_cache = torch.randn(case.batch, case.kv_heads, case.max_seq, case.dim, generator=g).to(dtype)
+    angles = torch.randn(1 if case.shared_cos else case.batch, 1, case.dim // 2, generator=g)
+    emb = torch.cat((angles, angles), dim=-1)
+    return q_raw, k_raw, v_raw, emb.cos().to(dtype), emb.sin().to(dtype), k_cache, v_cache

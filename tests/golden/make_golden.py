@@ -311,6 +311,36 @@ def host_contract_goldens(ref) -> None:
     (HERE / "host_contract.json").write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n")
 
 
+def rope_append_goldens(ref_root: Path) -> None:
+    """RoPE + append through the reference's own safe path (`_apply_qwen_rope` + `copy_`,
+    benchmarks/profile_seed_only_fused_rope_parity.py:24-30, 97-102), on CPU tensors."""
+
+    import importlib
+
+    parity = importlib.import_module("benchmarks.profile_seed_only_fused_rope_parity")
+    out = {}
+    for name, case in cases.ROPE_APPEND_CASES.items():
+        q_raw, k_raw, v_raw, cos, sin, k_cache, v_cache = cases.rope_append_inputs(case)
+        cos_ref = cos.expand(case.batch, -1, -1) if case.shared_cos else cos
+        sin_ref = sin.expand(case.batch, -1, -1) if case.shared_cos else sin
+        q_rot = parity._apply_qwen_rope(q_raw, cos_ref, sin_ref)
+        k_rot = parity._apply_qwen_rope(k_raw, cos_ref, sin_ref)
+        k_ref, v_ref = k_cache.clone(), v_cache.clone()
+        positions = case.positions if len(case.positions) > 1 else case.positions * case.batch
+        for b, pos in enumerate(positions):
+            k_ref[b, :, pos : pos + 1, :].copy_(k_rot[b])
+            v_ref[b, :, pos : pos + 1, :].copy_(v_raw[b])
+        # Stored: the rotated query, the rows the reference wrote, and how many cache elements
+        # differ from the input caches afterwards (only the written rows may).
+        rows = torch.tensor(positions)
+        idx = torch.arange(case.batch)
+        out[f"{name}/q_rot"] = _np(q_rot.float())
+        out[f"{name}/k_rows"] = _np(k_ref[idx, :, rows, :].float())
+        out[f"{name}/v_rows"] = _np(v_ref[idx, :, rows, :].float())
+        out[f"{name}/changed"] = np.array([int((k_ref != k_cache).sum()), int((v_ref != v_cache).sum())])
+    np.savez_compressed(HERE / "rope_append_reference_outputs.npz", **out)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", default="/root/reference")
@@ -324,6 +354,7 @@ def main() -> None:
     paged_goldens(ref)
     seed_goldens(ref, ref_root)
     host_contract_goldens(ref)
+    rope_append_goldens(ref_root)
     print("fixtures written to", HERE)
 
 

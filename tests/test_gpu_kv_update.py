@@ -1,0 +1,169 @@
+"""GPU parity of the KV-cache update step (rotary embedding + append), through the C ABI.
+
+The kernel must reproduce the reference's safe path bit for bit: the stored outputs of the
+reference (``tests/golden/rope_append_reference_outputs.npz``) and the oracle restatement of it
+on the same seeded inputs, for contiguous and paged caches; then a short decode loop
+(append, decode, append, ...) must agree with the oracle's loop.
+"""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import streamattn_b200 as sa
+from oracle import cpu_oracle, torch_port
+from streamattn_b200 import native
+from streamattn_b200.kv_update import PagedKVWriter, PagePool, append_kv, paged_append_kv
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden" / "rope_append_reference_outputs.npz"
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; refusing to skip")
+    return torch.device("cuda:0")
+
+
+def _positions(case):
+    return list(case.positions if len(case.positions) > 1 else case.positions * case.batch)
+
+
+@pytest.mark.parametrize("kv_layout", ["BHND", "BNHD"])
+@pytest.mark.parametrize("name", list(cases.ROPE_APPEND_CASES))
+def test_rope_append_contiguous_bit_exact(dev, name, kv_layout):
+    case = cases.ROPE_APPEND_CASES[name]
+    golden = np.load(GOLDEN)
+    q_raw, k_raw, v_raw, cos, sin, k_cache, v_cache = cases.rope_append_inputs(case)
+    want_k, want_v = k_cache.clone(), v_cache.clone()
+    want_q = torch_port.rope_append(q_raw, k_raw, v_raw, cos, sin, want_k, want_v, _positions(case))
+
+    def cache_to_dev(t):
+        return (t.transpose(1, 2).contiguous() if kv_layout == "BNHD" else t.clone()).to(dev)
+
+    kc, vc = cache_to_dev(k_cache), cache_to_dev(v_cache)
+    positions = torch.tensor(case.positions, dtype=torch.int64, device=dev)   # one entry or one per row
+    lengths_out = torch.zeros(case.batch, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    q_rot = append_kv(kc, vc, k_raw.to(dev), v_raw.to(dev), positions, kv_layout=kv_layout, new_layout="BHND",
+                      cos=cos.to(dev), sin=sin.to(dev), query=q_raw.to(dev), query_layout="BHND",
+                      lengths_out=lengths_out, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got_k = kc.transpose(1, 2) if kv_layout == "BNHD" else kc
+    got_v = vc.transpose(1, 2) if kv_layout == "BNHD" else vc
+    assert torch.equal(q_rot.cpu(), want_q)
+    assert torch.equal(got_k.cpu(), want_k) and torch.equal(got_v.cpu(), want_v)
+    assert lengths_out.cpu().tolist() == [p + 1 for p in _positions(case)]
+    # ... and the reference's stored outputs themselves.
+    idx, rows = torch.arange(case.batch), torch.tensor(_positions(case))
+    assert np.array_equal(q_rot.float().cpu().numpy(), golden[f"{name}/q_rot"])
+    assert np.array_equal(got_k.cpu()[idx, :, rows, :].float().numpy(), golden[f"{name}/k_rows"])
+    assert np.array_equal(got_v.cpu()[idx, :, rows, :].float().numpy(), golden[f"{name}/v_rows"])
+
+
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_append_paged_bit_exact_and_lengths_advance(dev, layout, dtype):
+    g = torch.Generator().manual_seed(21)
+    batch, q_heads, kv_heads, dim, page, max_pages = 3, 8, 2, 64, 16, 4
+    num_pages = batch * max_pages
+    shape = (num_pages, page, kv_heads, dim) if layout == "NHD" else (num_pages, kv_heads, page, dim)
+    kp = torch.randn(shape, generator=g).to(dtype)
+    vp = torch.randn(shape, generator=g).to(dtype)
+    table = torch.randperm(num_pages, generator=g).to(torch.int32).view(batch, max_pages)
+    lengths = torch.tensor([5, 16, 47], dtype=torch.int32)       # next token: mid page, page start, page end
+    q_raw = torch.randn(batch, 1, q_heads, dim, generator=g).to(dtype)
+    k_raw = torch.randn(batch, 1, kv_heads, dim, generator=g).to(dtype)
+    v_raw = torch.randn(batch, 1, kv_heads, dim, generator=g).to(dtype)
+    angles = torch.randn(batch, 1, dim // 2, generator=g)
+    emb = torch.cat((angles, angles), dim=-1)
+    cos, sin = emb.cos().to(dtype), emb.sin().to(dtype)
+    want_k, want_v = kp.clone(), vp.clone()
+    want_q = torch_port.paged_rope_append(q_raw.transpose(1, 2), k_raw.transpose(1, 2), v_raw.transpose(1, 2), cos, sin,
+                                          want_k, want_v, table, lengths.tolist(), layout=layout)
+    cache = sa.PagedKVCache(key=kp.to(dev), value=vp.to(dev), page_table=table.to(dev),
+                            sequence_lengths=lengths.to(dev), layout=layout)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    q_rot = paged_append_kv(cache, k_raw.to(dev), v_raw.to(dev), cos=cos.to(dev), sin=sin.to(dev),
+                            query=q_raw.to(dev), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(q_rot.cpu(), want_q.transpose(1, 2))
+    assert torch.equal(cache.key.cpu(), want_k) and torch.equal(cache.value.cpu(), want_v)
+    assert cache.sequence_lengths.cpu().tolist() == [6, 17, 48]  # advanced in place on the device
+
+
+def test_append_reports_bad_position_and_unassigned_page(dev):
+    batch, kv_heads, dim, page, max_pages = 2, 2, 64, 16, 2
+    kp = torch.zeros(4, page, kv_heads, dim, dtype=torch.bfloat16, device=dev)
+    vp = torch.zeros_like(kp)
+    table = torch.tensor([[0, -1], [1, 2]], dtype=torch.int32, device=dev)
+    lengths = torch.tensor([16, 32], dtype=torch.int32, device=dev)   # row 0: page not assigned; row 1: cache full
+    cache = sa.PagedKVCache(key=kp, value=vp, page_table=table, sequence_lengths=lengths, layout="NHD")
+    ones = torch.ones(batch, 1, kv_heads, dim, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    paged_append_kv(cache, ones, ones, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == native.SA_DEV_BAD_PAGE | native.SA_DEV_BAD_POSITION
+    assert float(kp.abs().sum()) == 0.0 and float(vp.abs().sum()) == 0.0     # nothing written
+    assert lengths.cpu().tolist() == [16, 32]                                 # skipped rows do not advance
+    with pytest.raises(ValueError, match="one entry or one per batch row"):
+        append_kv(torch.zeros(2, 2, 8, 64, device=dev), torch.zeros(2, 2, 8, 64, device=dev),
+                  torch.zeros(2, 2, 1, 64, device=dev), torch.zeros(2, 2, 1, 64, device=dev),
+                  torch.zeros(3, dtype=torch.int64, device=dev))
+
+
+def test_decode_loop_append_then_decode_matches_oracle(dev):
+    """Five steps of append (with RoPE) + paged exact decode on a bound plan, no host sync inside
+    the step: the plan must see each new token, pages are assigned ahead by the host allocator."""
+
+    g = torch.Generator().manual_seed(33)
+    batch, q_heads, kv_heads, dim, page, max_pages = 2, 8, 2, 64, 16, 6
+    num_pages = batch * max_pages
+    start = [30, 47]
+    kp = torch.zeros(num_pages, kv_heads, page, dim, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    table = torch.full((batch, max_pages), -1, dtype=torch.int32)
+    pool = PagePool(num_pages)
+    for b, n in enumerate(start):
+        ids = pool.allocate(-(-n // page))
+        table[b, : len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        for t in range(n):
+            kp[ids[t // page], :, t % page] = torch.randn(kv_heads, dim, generator=g).bfloat16()
+            vp[ids[t // page], :, t % page] = torch.randn(kv_heads, dim, generator=g).bfloat16()
+    ref_k, ref_v, ref_table = kp.clone(), vp.clone(), table.clone()
+    cache = sa.PagedKVCache(key=kp.to(dev), value=vp.to(dev), page_table=table.to(dev),
+                            sequence_lengths=torch.tensor(start, dtype=torch.int32, device=dev), layout="HND")
+    writer = PagedKVWriter.attach(cache, pool)
+    q_dev = torch.zeros(batch, 1, q_heads, dim, dtype=torch.bfloat16, device=dev)
+    plan = sa.PagedExactDecodePlan.build(q_dev, cache, validate_metadata=False)
+    lengths = list(start)
+    for step in range(5):
+        q_raw = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16()
+        k_raw = torch.randn(batch, 1, kv_heads, dim, generator=g).bfloat16()
+        v_raw = torch.randn(batch, 1, kv_heads, dim, generator=g).bfloat16()
+        angles = torch.randn(batch, 1, dim // 2, generator=g)
+        emb = torch.cat((angles, angles), dim=-1)
+        cos, sin = emb.cos().bfloat16(), emb.sin().bfloat16()
+        # device: assign pages, append + rotate q straight into the plan's query buffer, decode
+        writer.append(k_raw.to(dev), v_raw.to(dev), cos=cos.to(dev), sin=sin.to(dev), query=q_raw.to(dev),
+                      query_out=q_dev)
+        out = plan.run().clone()
+        # oracle: same step on the CPU
+        ref_table = cache.page_table.cpu()
+        q_rot = torch_port.paged_rope_append(q_raw.transpose(1, 2), k_raw.transpose(1, 2), v_raw.transpose(1, 2),
+                                             cos, sin, ref_k, ref_v, ref_table, lengths, layout="HND")
+        lengths = [n + 1 for n in lengths]
+        want = cpu_oracle.paged_decode(q_rot.transpose(1, 2).contiguous(), ref_k, ref_v, ref_table,
+                                       torch.tensor(lengths, dtype=torch.int32), layout="HND")
+        want = want[0] if isinstance(want, tuple) else want
+        diff = (out.float().cpu() - want.float()).abs()
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3, (step, float(diff.max()))
+        assert torch.equal(cache.key.cpu(), ref_k) and torch.equal(cache.value.cpu(), ref_v)
+    assert writer.lengths == lengths == cache.sequence_lengths.cpu().tolist()
+    assert plan.device_status() == 0
