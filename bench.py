@@ -210,14 +210,15 @@ def build_loop_c2(device):
     q_rot = torch.empty_like(q_raw)
     plan = sa.ExactDecodePlan.build(q_rot, k, v, kv_layout="BHND", seq_lens=lens,
                                     dynamic_schedule=SCHEDULE["dynamic"])
+    append = sa.AppendKVPlan.build(k, v, k_new, v_new, lens, kv_layout="BHND", cos=cos, sin=sin, query=q_raw,
+                                   query_out=q_rot, query_layout="BNHD", lengths_out=lens)
     state = {"steps": 0}
 
     def run():
         if start + state["steps"] >= N:  # cache full: start the rows over (rare, outside the steady state)
             lens.fill_(start)
             state["steps"] = 0
-        sa.append_kv(k, v, k_new, v_new, lens, kv_layout="BHND", cos=cos, sin=sin, query=q_raw, query_out=q_rot,
-                     query_layout="BNHD", lengths_out=lens)
+        append.run()
         state["steps"] += 1
         return plan.run()
 

@@ -52,7 +52,7 @@ from .paged import (
     choose_paged_exact_splits,
     stream_attn_paged_exact_decode,
 )
-from .kv_update import PagedKVWriter, PagePool, append_kv, paged_append_kv
+from .kv_update import AppendKVPlan, PagedKVWriter, PagePool, append_kv, paged_append_kv
 from .seed_schedule import policy_seed_blocks, seed_indices, seed_token_indices_from_blocks
 
 # ``import streamattn_b200 as stream_attn; stream_attn.decode(...)``

@@ -106,29 +106,9 @@ def append_kv(key_cache: torch.Tensor, value_cache: torch.Tensor, key_new: torch
     position is outside the cache; such rows are skipped.
     """
 
-    device = native.require_cuda(key_cache, value_cache, key_new, value_new, positions, cos, sin, query, query_out,
-                                 lengths_out, status)
-    if key_cache.dtype not in native.SA_DTYPE or any(t.dtype != key_cache.dtype for t in (value_cache, key_new, value_new)):
-        raise ValueError("caches and new rows must share a dtype of bf16, fp16 or fp32")
-    kv_heads, kv_len, sb, sn, sh = native._kv_geometry(key_cache, value_cache, kv_layout)
-    batch, dim = int(key_cache.shape[0]), int(key_cache.shape[3])
-    axis = _heads_axis(new_layout or kv_layout)
-    nb, nh, nd, new_sb, new_sh = _rows(key_new, axis, "key_new")
-    if (nb, nh, nd) != (batch, kv_heads, dim) or value_new.shape != key_new.shape or value_new.stride() != key_new.stride():
-        raise ValueError("key_new / value_new must be one token of the cache's batch, KV heads and head_dim")
-    pos_dtype, num_positions = _positions(positions, batch, lengths_out)
-    cos, sin, rope_sb = _rope_args(cos, sin, batch, dim, key_cache.dtype)
-    query, query_out, q_heads, qs = _query_args(query, query_out, query_layout, batch, dim, key_cache.dtype)
-    with torch.cuda.device(device):
-        rc = native.load().sa_append_kv(
-            native._ptr(key_new), native._ptr(value_new), native._ptr(key_cache), native._ptr(value_cache),
-            native._ptr(positions), pos_dtype, num_positions, native._ptr(lengths_out),
-            native._ptr(cos), native._ptr(sin), rope_sb,
-            native._ptr(query), native._ptr(query_out), q_heads, *qs,
-            batch, kv_heads, dim, kv_len, new_sb, new_sh, sb, sn, sh,
-            native.SA_DTYPE[key_cache.dtype], native._ptr(status), native.stream_handle(device))
-    native.check(rc)
-    return query_out
+    return AppendKVPlan.build(key_cache, value_cache, key_new, value_new, positions, kv_layout=kv_layout,
+                              new_layout=new_layout, cos=cos, sin=sin, query=query, query_out=query_out,
+                              query_layout=query_layout, lengths_out=lengths_out, status=status).run()
 
 
 def paged_append_kv(cache: PagedKVCache, key_new: torch.Tensor, value_new: torch.Tensor, *,
@@ -146,6 +126,84 @@ def paged_append_kv(cache: PagedKVCache, key_new: torch.Tensor, value_new: torch
     through ``status`` (``SA_DEV_BAD_PAGE``) and the row is skipped.
     """
 
+    return AppendKVPlan.build_paged(cache, key_new, value_new, positions=positions, advance_lengths=advance_lengths,
+                                    new_layout=new_layout, cos=cos, sin=sin, query=query, query_out=query_out,
+                                    query_layout=query_layout, status=status).run()
+
+
+class AppendKVPlan:
+    """A validated, bound cache update: ``run()`` is one native call (no checks, no allocation).
+
+    The tensors are bound by address, like the decode plans: refill ``key_new`` / ``value_new`` /
+    ``query`` / ``cos`` / ``sin`` in place between runs; positions and lengths are read on the
+    device at run time.
+    """
+
+    def __init__(self, fn_name: str, args: tuple, device: torch.device, keep: tuple, query_out) -> None:
+        self._fn = getattr(native.load(), fn_name)
+        self._args = args
+        self._device = device
+        self._device_index = device.index if device.index is not None else torch.cuda.current_device()
+        self._keep = keep
+        self.query_out = query_out
+
+    def run(self) -> Optional[torch.Tensor]:
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self._device_index):
+                rc = self._fn(*self._args, native._current_raw_stream(self._device_index))
+        else:
+            rc = self._fn(*self._args, native._current_raw_stream(self._device_index))
+        if rc:
+            native.check(rc)
+        return self.query_out
+
+    @classmethod
+    def build(cls, key_cache: torch.Tensor, value_cache: torch.Tensor, key_new: torch.Tensor,
+              value_new: torch.Tensor, positions: torch.Tensor, *, kv_layout: str = "BHND",
+              new_layout: Optional[str] = None, cos: Optional[torch.Tensor] = None,
+              sin: Optional[torch.Tensor] = None, query: Optional[torch.Tensor] = None,
+              query_out: Optional[torch.Tensor] = None, query_layout: str = "BNHD",
+              lengths_out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> "AppendKVPlan":
+        """Arguments as :func:`append_kv`."""
+
+        device = native.require_cuda(key_cache, value_cache, key_new, value_new, positions, cos, sin, query,
+                                     query_out, lengths_out, status)
+        dtype = key_cache.dtype
+        if dtype not in native.SA_DTYPE or any(t.dtype != dtype for t in (value_cache, key_new, value_new)):
+            raise ValueError("caches and new rows must share a dtype of bf16, fp16 or fp32")
+        kv_heads, kv_len, sb, sn, sh = native._kv_geometry(key_cache, value_cache, kv_layout)
+        batch, dim = int(key_cache.shape[0]), int(key_cache.shape[3])
+        nb, nh, nd, new_sb, new_sh = _rows(key_new, _heads_axis(new_layout or kv_layout), "key_new")
+        if (nb, nh, nd) != (batch, kv_heads, dim) or value_new.shape != key_new.shape \
+                or value_new.stride() != key_new.stride():
+            raise ValueError("key_new / value_new must be one token of the cache's batch, KV heads and head_dim")
+        pos_dtype, num_positions = _positions(positions, batch, lengths_out)
+        cos, sin, rope_sb = _rope_args(cos, sin, batch, dim, dtype)
+        query, query_out, q_heads, qs = _query_args(query, query_out, query_layout, batch, dim, dtype)
+        args = (native._ptr(key_new), native._ptr(value_new), native._ptr(key_cache), native._ptr(value_cache),
+                native._ptr(positions), pos_dtype, num_positions, native._ptr(lengths_out),
+                native._ptr(cos), native._ptr(sin), rope_sb,
+                native._ptr(query), native._ptr(query_out), q_heads, *qs,
+                batch, kv_heads, dim, kv_len, new_sb, new_sh, sb, sn, sh,
+                native.SA_DTYPE[dtype], native._ptr(status))
+        keep = (key_cache, value_cache, key_new, value_new, positions, lengths_out, cos, sin, query, query_out, status)
+        return cls("sa_append_kv", args, device, keep, query_out)
+
+    @classmethod
+    def build_paged(cls, cache: PagedKVCache, key_new: torch.Tensor, value_new: torch.Tensor, *,
+                    positions: Optional[torch.Tensor] = None, advance_lengths: bool = True,
+                    new_layout: str = "BNHD", cos: Optional[torch.Tensor] = None,
+                    sin: Optional[torch.Tensor] = None, query: Optional[torch.Tensor] = None,
+                    query_out: Optional[torch.Tensor] = None, query_layout: str = "BNHD",
+                    status: Optional[torch.Tensor] = None) -> "AppendKVPlan":
+        """Arguments as :func:`paged_append_kv`."""
+
+        return cls(*_paged_call(cache, key_new, value_new, positions, advance_lengths, new_layout, cos, sin, query,
+                                query_out, query_layout, status))
+
+
+def _paged_call(cache, key_new, value_new, positions, advance_lengths, new_layout, cos, sin, query, query_out,
+                query_layout, status):
     if positions is None:
         positions = cache.sequence_lengths
     lengths_out = cache.sequence_lengths if advance_lengths else None
@@ -172,17 +230,15 @@ def paged_append_kv(cache: PagedKVCache, key_new: torch.Tensor, value_new: torch
     pos_dtype, num_positions = _positions(positions, batch, lengths_out)
     cos, sin, rope_sb = _rope_args(cos, sin, batch, dim, dtype)
     query, query_out, q_heads, qs = _query_args(query, query_out, query_layout, batch, dim, dtype)
-    with torch.cuda.device(device):
-        rc = native.load().sa_paged_append_kv(
-            native._ptr(key_new), native._ptr(value_new), native._ptr(cache.key), native._ptr(cache.value),
+    args = (native._ptr(key_new), native._ptr(value_new), native._ptr(cache.key), native._ptr(cache.value),
             native._ptr(cache.page_table), native.SA_INDEX[cache.page_table.dtype],
             native._ptr(positions), pos_dtype, num_positions, native._ptr(lengths_out),
             native._ptr(cos), native._ptr(sin), rope_sb,
             native._ptr(query), native._ptr(query_out), q_heads, *qs,
             batch, kv_heads, dim, page_size, max_pages, num_pages, native.SA_LAYOUT[layout], new_sb, new_sh,
-            native.SA_DTYPE[dtype], native._ptr(status), native.stream_handle(device))
-    native.check(rc)
-    return query_out
+            native.SA_DTYPE[dtype], native._ptr(status))
+    keep = (cache, key_new, value_new, positions, lengths_out, cos, sin, query, query_out, status)
+    return "sa_paged_append_kv", args, device, keep, query_out
 
 
 class PagePool:
@@ -290,4 +346,4 @@ class PagedKVWriter:
         self.cache.page_table[row].fill_(-1)
 
 
-__all__ = ["append_kv", "paged_append_kv", "PagePool", "PagedKVWriter"]
+__all__ = ["append_kv", "paged_append_kv", "AppendKVPlan", "PagePool", "PagedKVWriter"]

@@ -167,3 +167,49 @@ def test_decode_loop_append_then_decode_matches_oracle(dev):
         assert torch.equal(cache.key.cpu(), ref_k) and torch.equal(cache.value.cpu(), ref_v)
     assert writer.lengths == lengths == cache.sequence_lengths.cpu().tolist()
     assert plan.device_status() == 0
+
+
+def test_bound_append_plan_and_decode_replay_in_a_cuda_graph(dev):
+    """append + decode captured once and replayed: positions and lengths live on the device, so
+    every replay writes the next token and attends to one token more."""
+
+    g = torch.Generator().manual_seed(44)
+    batch, q_heads, kv_heads, dim, cap, start = 2, 8, 2, 64, 256, 100
+    k = torch.randn(batch, kv_heads, cap, dim, generator=g).bfloat16()
+    v = torch.randn(batch, kv_heads, cap, dim, generator=g).bfloat16()
+    q_raw = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16()
+    k_new = torch.randn(batch, kv_heads, 1, dim, generator=g).bfloat16()
+    v_new = torch.randn(batch, kv_heads, 1, dim, generator=g).bfloat16()
+    kd, vd = k.to(dev), v.to(dev)
+    lens = torch.full((batch,), start, dtype=torch.int32, device=dev)
+    q_dev = torch.empty(batch, 1, q_heads, dim, dtype=torch.bfloat16, device=dev)
+    append = sa.AppendKVPlan.build(kd, vd, k_new.to(dev), v_new.to(dev), lens, kv_layout="BHND",
+                                   query=q_raw.to(dev), query_out=q_dev, lengths_out=lens)
+    plan = sa.ExactDecodePlan.build(q_dev, kd, vd, kv_layout="BHND", seq_lens=lens)
+    side = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        append.run()
+        plan.run()
+        side.synchronize()
+        lens.fill_(start)                         # undo the warm-up step
+        kd.copy_(k)
+        vd.copy_(v)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            append.run()
+            plan.run()
+    steps = 3
+    for _ in range(steps):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert lens.cpu().tolist() == [start + steps] * batch
+    want_k, want_v = k.clone(), v.clone()
+    for t in range(steps):
+        torch_port.rope_append(None, k_new, v_new, None, None, want_k, want_v, [start + t] * batch)
+    assert torch.equal(kd.cpu(), want_k) and torch.equal(vd.cpu(), want_v)
+    n = start + steps
+    want = cpu_oracle.exact_decode(q_raw, want_k[:, :, :n].transpose(1, 2).contiguous(),
+                                   want_v[:, :, :n].transpose(1, 2).contiguous())
+    diff = (plan.output.float().cpu() - want.float()).abs()
+    assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3
