@@ -51,10 +51,11 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until a capture exists for the workload).
-# The reference's published number for the same metric and shape, from its own artifacts as
-# listed in BASELINE.md: config 2 on one H100 (not a B200), 96.3 us per call = 2787 GB/s.
+# The reference's published number for the same metric and shape (its serving-gate artifact
+# artifacts/gate0/transposed_wgmma_exact_promoted_serving_gate_h100_20260818.json): config 2 on
+# one H100 (not a B200), 96.3 us per call = 2787 GB/s.
 PUBLISHED_GBS = {"exact_c2": 268435456 / 96.3e-6 / 1e9}
-NCU_TRAFFIC_BYTES = {"exact_c2": 272.3e6, "paged_c3": 170.9e6}
+NCU_TRAFFIC_BYTES = {"exact_c2": 272.3e6, "paged_c3": 170.9e6, "cp_c5": 8 * 541.7e6}  # cp_c5: whole row, divided by N below
 
 
 def measured_hbm_peak():
@@ -137,6 +138,15 @@ def _randn_bf16(shape, seed, device):
 # --------------------------------------------------------------------------
 
 SCHEDULE = {"dynamic": None}  # set from --schedule: None follows STREAMATTN_B200_SCHEDULE (default static)
+
+
+def traffic_per_launch(workload: str, world: int):
+    """DRAM read+write bytes of one launch of the dominant kernel (from the ncu captures under profiles/)."""
+
+    total = NCU_TRAFFIC_BYTES.get(workload)
+    if total is None:
+        return None
+    return total / world if workload == "cp_c5" else total
 
 
 def schedule_name(workload: str) -> str:
@@ -250,10 +260,10 @@ def build_seed_c4(device):
     return plan.run, q, out, info, plan
 
 
-def build_cp_c5(device, rank, world, exchange="auto"):
+def build_cp_c5(device, rank, world, exchange="auto", kv_len=1048576):
     from streamattn_b200.context_parallel import ContextParallelExactDecode, shard_bounds
 
-    Hq, Hkv, D, N = 32, 8, 128, 1048576
+    Hq, Hkv, D, N = 32, 8, 128, int(kv_len)
     chunk = 65536
     lo, hi = shard_bounds(N, world, rank)
     q = _randn_bf16((1, 1, Hq, D), 100, device)
@@ -347,6 +357,9 @@ def main() -> None:
     ap.add_argument("--schedule", default="default", choices=["default", "static", "dynamic"],
                     help="tile schedule of the exact/paged plans: static is bit-reproducible (the default), "
                          "dynamic claims tiles from a device counter")
+    ap.add_argument("--cp-kv-len", type=int, default=1048576,
+                    help="cp_c5 only: total tokens of the row (131072 on one GPU = the shard one of 8 GPUs holds; "
+                         "used for small profiler captures)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + the timed region (for runs under ncu): no e2e, CPU or clock legs")
     args = ap.parse_args()
@@ -403,7 +416,7 @@ def main() -> None:
     elif workload == "loop_c2":
         run, q_dev, out_dev, info, plan = build_loop_c2(device)
     else:
-        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world, args.exchange)
+        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world, args.exchange, args.cp_kv_len)
     alg_bytes = info.pop("bytes")
     launches = info.pop("launches")
 
@@ -526,7 +539,7 @@ def main() -> None:
                        "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2"),
                        "timing": "CUDA events around K back-to-back calls, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(workload),
+                         "frac": achieved / peak, "traffic": traffic_per_launch(workload, world),
                          "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8tbs": achieved / 8000.0,
                          "kernel": info["kernel"], "algorithmic_bytes_per_launch": per_gpu_bytes},
             "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "us_per_call": e2e_s * 1e6,

@@ -343,7 +343,7 @@ def rope_append_goldens(ref_root: Path) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of the StreamAttn reference checkout")
     args = parser.parse_args()
     ref_root = Path(args.reference)
     sys.path.insert(0, str(ref_root))
