@@ -67,64 +67,114 @@ def measured_hbm_peak():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while a region runs."""
+    """SM clock and throttle reasons while a region runs, sampled by an ``nvidia-smi`` child process.
+
+    The sampler is a separate process on purpose: a sampling thread inside the timed process
+    (NVML queries every few ms, competing for the interpreter lock with the launch loop) was
+    measured to slow lock-stepped multi-GPU steps by 15 % at 8 ranks, because a launch loop that
+    hiccups on one rank stalls every rank.  ``nvidia-smi -lms`` samples every ``period_ms``; the
+    lines whose time stamp falls inside [begin(), end()] are summarised.
+    """
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+    QUERY = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active"
 
-    def __init__(self, index: int, period_s: float = 0.004) -> None:
-        self.samples = []
-        self.reasons = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        self._period = period_s
+    def __init__(self, index: int, period_ms: int = 100) -> None:
+        self.index = index
+        self.period_ms = period_ms
+        self._proc = None
+        self._log = None
+        self._t0 = self._t1 = None
+        self._edge_samples = []  # NVML readings taken at begin() and end() by this process
+
+    def start(self) -> "ClockSampler":
+        import shutil
+        import subprocess
+        import tempfile
+
+        exe = shutil.which("nvidia-smi")
+        if exe is not None:
+            self._log = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            try:
+                self._proc = subprocess.Popen(
+                    [exe, "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                     "-lms", str(self.period_ms)], stdout=self._log, stderr=subprocess.DEVNULL)
+            except OSError:
+                self._proc = None
+        return self
+
+    def _nvml_once(self) -> None:
         try:
             import pynvml
 
             pynvml.nvmlInit()
-            self._nvml = pynvml
-            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
-        except Exception:
-            self._nvml = None
-
-    def _sample_once(self) -> None:
-        nv = self._nvml
-        try:
-            self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
-            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
-            bits = int(get(self._handle))
-            for bit, name in self.REASONS.items():
-                if bits & bit:
-                    self.reasons.add(name)
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            get = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self._edge_samples.append((int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                       int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                       int(get(handle))))
         except Exception:
             pass
 
-    def _loop(self) -> None:
-        while not self._stop.is_set():
-            self._sample_once()
-            time.sleep(self._period)
+    def begin(self) -> None:
+        import datetime
 
-    def __enter__(self):
-        if self._nvml is not None:
-            self._sample_once()
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
-        return self
+        self._t0 = datetime.datetime.now()
 
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
-            self._sample_once()
+    def sample_under_load(self) -> None:
+        """One direct NVML reading; call it while the steps just enqueued are still running."""
+
+        self._nvml_once()
+
+    def end(self) -> None:
+        import datetime
+
+        self._t1 = datetime.datetime.now()
+
+    def stop(self) -> None:
+        if self._proc is not None:
+            self._proc.terminate()  # the exact child started above
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                self._proc.kill()
+            self._proc = None
 
     def summary(self) -> dict:
+        import datetime
+
+        samples, reasons, max_mhz = [], set(), None
+        if self._log is not None and self._t0 is not None and self._t1 is not None:
+            try:
+                self._log.flush()
+                self._log.seek(0)
+                for line in self._log.read().splitlines():
+                    parts = [x.strip() for x in line.split(",")]
+                    if len(parts) != 4:
+                        continue
+                    try:
+                        stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                        mhz, mx, bits = int(parts[1]), int(parts[2]), int(parts[3], 16)
+                    except ValueError:
+                        continue
+                    max_mhz = mx
+                    if self._t0 <= stamp <= self._t1:
+                        samples.append(mhz)
+                        reasons.update(name for bit, name in self.REASONS.items() if bits & bit)
+            except Exception:
+                pass
+        for mhz, mx, bits in self._edge_samples:
+            samples.append(mhz)
+            max_mhz = mx
+            reasons.update(name for bit, name in self.REASONS.items() if bits & bit)
         return {
-            "sm_mhz": statistics.median(self.samples) if self.samples else None,
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.samples),
+            "sm_mhz": statistics.median(samples) if samples else None,
+            "sm_max_mhz": max_mhz,
+            "reasons": sorted(reasons),
+            "samples": len(samples),
+            "sampler": f"nvidia-smi -lms {self.period_ms} (child process) + one NVML reading under load",
         }
 
 
@@ -392,6 +442,7 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    clocks = ClockSampler(local_rank).start()  # child process: it comes up while the inputs are built
     distributed = world > 1
     if distributed:
         import torch.distributed as dist
@@ -440,16 +491,22 @@ def main() -> None:
     for _ in range(warmup):
         run()
     barrier()
-    with ClockSampler(local_rank) as clocks:
-        elapsed = time_region(run, args.steps, device)
-        if len(clocks.samples) < 4 and not args.profile:  # very short region: keep the same kernel busy until NVML has samples
-            t_end = time.perf_counter() + 0.3
-            while time.perf_counter() < t_end:
-                for _ in range(50):
-                    run()
-                torch.cuda.synchronize(device)
+    clocks.begin()
+    elapsed = time_region(run, args.steps, device)
     barrier()
     elapsed = max_over_ranks(elapsed)
+    if not args.profile:
+        # Short regions: keep the same step running (untimed) so that the 100 ms sampler sees the
+        # GPU under this very load a few times.  Every rank runs the same number of extra steps
+        # (the count follows from the agreed time), as lock-stepped ranks must.
+        extra = int(max(0.0, 0.6 - elapsed) / (elapsed / args.steps))
+        for _ in range(extra):
+            run()
+        clocks.sample_under_load()
+        torch.cuda.synchronize(device)
+    clocks.end()
+    clocks.stop()
+    barrier()
     step_s = elapsed / args.steps
 
     if args.profile:

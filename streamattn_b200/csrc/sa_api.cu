@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -698,6 +699,9 @@ sa_plan_t *sa_cp_fused_plan_create(const void *q, const void *k, const void *v, 
     plan->cp.gather_floats_per_parity = l.gather_floats_per_parity;
     plan->cp.flags_offset = l.flags_offset;
     plan->cp.final_out = out;
+#ifdef SA_TIMELINE
+    if (const char *e = std::getenv("SA_CP_DEBUG")) plan->cp.debug = std::atoi(e);
+#endif
     return plan;
 }
 

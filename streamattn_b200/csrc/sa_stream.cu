@@ -66,6 +66,9 @@ struct StreamParams {
 #if SA_TIMELINE == 2
 #define SA_PSTAMP(i) SA_STAMP_RAW(i)
 #define SA_STAMP(i) do { if ((i) < 2) SA_STAMP_RAW(i); } while (0)
+#elif SA_TIMELINE == 3  // context-parallel tail: slots 1, 2, 7 = rows staged, rows sent, pair finished
+#define SA_CSTAMP(i) SA_STAMP_RAW(i)
+#define SA_STAMP(i) do { if ((i) != 1 && (i) != 7) SA_STAMP_RAW(i); } while (0)
 #else
 #define SA_STAMP(i) SA_STAMP_RAW(i)
 #endif
@@ -74,6 +77,9 @@ struct StreamParams {
 #endif
 #ifndef SA_PSTAMP
 #define SA_PSTAMP(i) do { } while (0)
+#endif
+#ifndef SA_CSTAMP
+#define SA_CSTAMP(i) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -160,12 +166,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, u
 }
 
 // Context-parallel exchange words: {value, step} written and read as one 8-byte access.
-__device__ __forceinline__ void cp_store(uint2 *dst, float value, uint32_t step)
-{
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(value)), "r"(step)
-                 : "memory");
-}
-
 __device__ __forceinline__ uint2 cp_load(const uint2 *src)
 {
     uint2 v;
@@ -211,13 +211,23 @@ template <> struct Mma<__half> {
 // stores are what NVLink handles worst.  Each 8-byte half carries its own step tag, so the copy
 // needs no ordering or atomicity beyond that of an aligned 8-byte access.
 template <int NTHREADS>
-__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, const uint2 *stage, size_t start, int words, int tid)
+__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, const uint2 *stage, size_t start, size_t rank_stride,
+                                               int words, int tid)
 {
     const uint4 *src = reinterpret_cast<const uint4 *>(stage);
     for (int i = tid; i < words / 2; i += NTHREADS) {  // `start` and `words` are even: 16-byte pieces
         const uint4 v = src[i];
-        for (int r = 0; r < cp.world; ++r) {
+        for (int k = 0; k < cp.world; ++k) {
+            // Every rank starts with its right-hand neighbour, so the ranks - which finish a step
+            // at about the same time - do not all write to the same destination at once.
+            const int r = cp.rank + 1 + k < cp.world ? cp.rank + 1 + k : cp.rank + 1 + k - cp.world;
+#ifdef SA_CP_LOOPBACK  // debug builds: one GPU plays every rank (its rows land in all rank slots)
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[cp.rank]) + start +
+                                                   (static_cast<ptrdiff_t>(r) - cp.rank) * static_cast<ptrdiff_t>(rank_stride)) + i;
+#else
+            (void)rank_stride;
             uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[r]) + start) + i;
+#endif
             asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y),
                          "r"(v.z), "r"(v.w)
                          : "memory");
@@ -275,6 +285,9 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_
                         atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
                         break;
                     }
+#if defined(SA_TIMELINE) && SA_TIMELINE == 3
+                    if (waiting && (cp.debug & 2)) __nanosleep(300);  // experiment: poll less often
+#endif
                 }
                 float nb = big;
 #pragma unroll
@@ -340,7 +353,7 @@ __device__ __noinline__ void merge_pair_states(const float *first_slot, int64_t 
                                                float *sm, int tid)
 {
     constexpr int PART_STRIDE = D + 4;
-    constexpr int BATCH = 8;
+    constexpr int BATCH = 10;  // states per thread and pass: 20 split states (19 CTAs per pair at 8 pairs) in one pass
     const int parts = NTHREADS / items;
     const int part = tid / items;
     const int item = tid - part * items;
@@ -350,7 +363,7 @@ __device__ __noinline__ void merge_pair_states(const float *first_slot, int64_t 
     const float *src = first_slot + row * PART_STRIDE;
     float big = -INFINITY, total_l = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int i0 = part; active && i0 < nseg; i0 += parts * BATCH) {  // one pass up to 8 * parts states
+    for (int i0 = part; active && i0 < nseg; i0 += parts * BATCH) {  // one pass up to BATCH * parts states
         float4 o[BATCH];
         float2 ml[BATCH];
 #pragma unroll
@@ -1200,13 +1213,19 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
         if (p.cp.world > 0 && (nseg == 1 || s_last)) {
             __syncthreads();  // the pair's rows are complete in the staging area; the state areas are free
+            SA_CSTAMP(1);
             cp_broadcast_pair<NTHREADS>(
                 p.cp, cp_stage,
                 (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
                     (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0) * STATE_STRIDE,
-                group * STATE_STRIDE, tid);
+                static_cast<size_t>(p.batch) * p.q_heads * STATE_STRIDE, group * STATE_STRIDE, tid);
+#if defined(SA_TIMELINE) && SA_TIMELINE == 3
+            if (p.cp.debug & 1) __threadfence_system();  // experiment: push the peer stores out at once
+#endif
+            SA_CSTAMP(2);
             cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, static_cast<size_t>(p.batch) * p.q_heads, out_row0, items,
                                            states, tid);
+            SA_CSTAMP(7);
         }
         __syncthreads();  // the state areas and s_last are reused by the next segment
         SA_STAMP(6);

@@ -35,6 +35,9 @@ struct CpFuse {
     unsigned long long gather_floats_per_parity;
     unsigned long long flags_offset;
     void *final_out;  // [batch, q_heads, D] in the query dtype
+#ifdef SA_TIMELINE
+    int debug;        // debug builds only: experiment switches of the exchange
+#endif
 };
 
 struct StreamGeometry {
