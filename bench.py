@@ -346,7 +346,7 @@ def time_region(fn, steps, device):
     return start.elapsed_time(stop) * 1e-3
 
 
-def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1) -> dict:
+def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1, budget_s: float = 30.0) -> dict:
     """Reference CPU path (oracle port) on a bounded sample of the workload."""
 
     from oracle import torch_port
@@ -386,11 +386,15 @@ def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1) -> dict:
     for _ in range(warmup):
         fn()
     t0 = time.perf_counter()
-    for _ in range(steps):
+    done = 0
+    while done < steps:  # every requested step, unless the CPU time budget runs out first
         fn()
-    dt = (time.perf_counter() - t0) / steps
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
     return {"value": alg / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port", "sample": note,
-            "ms_per_sample": dt * 1e3}
+            "ms_per_sample": dt * 1e3, "samples_timed": done}
 
 
 def main() -> None:
@@ -426,10 +430,13 @@ def main() -> None:
     if args.impl == "reference":
         if rank != 0:
             return
-        base = cpu_baseline_sample(workload, steps=max(1, min(args.steps, 5)), warmup=min(warmup, 1))
+        # Every requested step is one bounded sample; a run that would exceed about two minutes of
+        # CPU time stops early and says how many steps it timed.
+        base = cpu_baseline_sample(workload, steps=max(1, args.steps), warmup=min(warmup, 3), budget_s=120.0)
         line = {
             "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample"],
+            "steps": base["samples_timed"], "steps_requested": args.steps, "warmup": min(warmup, 3),
+            "ms_per_step": base["ms_per_sample"],
             "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": workload, "sample": base["sample"]},
             "cpu_baseline": base,
