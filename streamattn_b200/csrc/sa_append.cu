@@ -39,8 +39,11 @@ __device__ __forceinline__ T rotate(const T *row, const T *cos_row, const T *sin
     return Elem<T>::from_float(Round<T>::add(a, b));
 }
 
+constexpr int kAppendThreads = 512;
+constexpr int kAppendBatch = 4;  // elements per thread whose loads are all in flight before any store
+
 template <typename T>
-__global__ void __launch_bounds__(256) append_kv_kernel(const __grid_constant__ AppendParams p)
+__global__ void __launch_bounds__(kAppendThreads) append_kv_kernel(const __grid_constant__ AppendParams p)
 {
     // Let the next kernel of the stream (normally the decode) be scheduled early, and wait for
     // everything launched before this kernel - the producer of k_new / v_new / q - to complete.
@@ -82,24 +85,43 @@ __global__ void __launch_bounds__(256) append_kv_kernel(const __grid_constant__ 
     const T *sin_row = rope ? static_cast<const T *>(p.sin) + b * p.rope_sb : nullptr;
     const int kv_items = p.kv_heads * dim;
     const int q_items = p.q_in != nullptr ? p.q_heads * dim : 0;
-    for (int i = tid; i < 2 * kv_items + q_items; i += blockDim.x) {
-        if (i < kv_items) {  // K row of head h
-            if (!valid) continue;
-            const int h = i / dim, d = i - h * dim;
-            const T *src = static_cast<const T *>(p.k_new) + b * p.new_sb + h * p.new_sh;
-            k_dst[h * head_stride + d] = rope ? rotate<T>(src, cos_row, sin_row, d, dim) : src[d];
-        } else if (i < 2 * kv_items) {  // V row of head h
-            if (!valid) continue;
-            const int j = i - kv_items;
-            const int h = j / dim, d = j - h * dim;
-            v_dst[h * head_stride + d] = static_cast<const T *>(p.v_new)[b * p.new_sb + h * p.new_sh + d];
-        } else {  // query row of head h
-            const int j = i - 2 * kv_items;
-            const int h = j / dim, d = j - h * dim;
-            const T *src = static_cast<const T *>(p.q_in) + b * p.qi_sb + h * p.qi_sh;
-            static_cast<T *>(p.q_out)[b * p.qo_sb + h * p.qo_sh + d] =
-                rope ? rotate<T>(src, cos_row, sin_row, d, dim) : src[d];
+    const int total = 2 * kv_items + q_items;
+    // The call is latency-bound (a few KB per row): every thread first requests all it needs for
+    // up to kAppendBatch elements, then stores them, so a row costs one round trip per pass.
+    for (int base = 0; base < total; base += kAppendThreads * kAppendBatch) {
+        T value[kAppendBatch];
+        T *dst[kAppendBatch];
+#pragma unroll
+        for (int e = 0; e < kAppendBatch; ++e) {
+            const int i = base + e * kAppendThreads + tid;
+            dst[e] = nullptr;
+            value[e] = Elem<T>::from_float(0.0f);
+            if (i >= total) continue;
+            if (i < kv_items) {  // K row of head h
+                const int h = i / dim, d = i - h * dim;
+                const T *src = static_cast<const T *>(p.k_new) + b * p.new_sb + h * p.new_sh;
+                if (valid) {
+                    value[e] = rope ? rotate<T>(src, cos_row, sin_row, d, dim) : src[d];
+                    dst[e] = k_dst + h * head_stride + d;
+                }
+            } else if (i < 2 * kv_items) {  // V row of head h
+                const int j = i - kv_items;
+                const int h = j / dim, d = j - h * dim;
+                if (valid) {
+                    value[e] = static_cast<const T *>(p.v_new)[b * p.new_sb + h * p.new_sh + d];
+                    dst[e] = v_dst + h * head_stride + d;
+                }
+            } else {  // query row of head h
+                const int j = i - 2 * kv_items;
+                const int h = j / dim, d = j - h * dim;
+                const T *src = static_cast<const T *>(p.q_in) + b * p.qi_sb + h * p.qi_sh;
+                value[e] = rope ? rotate<T>(src, cos_row, sin_row, d, dim) : src[d];
+                dst[e] = static_cast<T *>(p.q_out) + b * p.qo_sb + h * p.qo_sh + d;
+            }
         }
+#pragma unroll
+        for (int e = 0; e < kAppendBatch; ++e)
+            if (dst[e] != nullptr) *dst[e] = value[e];
     }
     if (p.lens_out != nullptr && valid) {
         // lens_out may be the positions array itself: every thread has read its position above.
@@ -115,7 +137,7 @@ template <typename T> cudaError_t launch_typed(const AppendParams &p, cudaStream
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(p.batch));
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(kAppendThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
