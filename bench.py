@@ -552,6 +552,17 @@ def main() -> None:
             e2e_stream.synchronize()
 
         e2e_mode = "plan bound to pinned host query/output: the kernel reads q and writes out over PCIe"
+    elif workload == "paged_c3":
+        import streamattn_b200 as sa
+
+        host_plan = sa.PagedExactDecodePlan.build(q_host, plan.cache, output=out_host, validate_metadata=False,
+                                                  dynamic_schedule=SCHEDULE["dynamic"])
+
+        def e2e_step():  # noqa: F811
+            host_plan.run()
+            e2e_stream.synchronize()
+
+        e2e_mode = "plan bound to pinned host query/output: the kernel reads q and writes out over PCIe"
 
     for _ in range(warmup):
         e2e_step()
@@ -560,7 +571,7 @@ def main() -> None:
     e2e_elapsed = max_over_ranks(time_region(e2e_step, e2e_steps, device))
     barrier()
     e2e_s = e2e_elapsed / e2e_steps
-    if workload in ("exact_c2", "exact_c2_bnhd"):
+    if workload in ("exact_c2", "exact_c2_bnhd", "paged_c3"):
         torch.testing.assert_close(out_host.float(), out_dev.float().cpu(), atol=2e-2, rtol=0)
 
     status = plan.device_status() if hasattr(plan, "device_status") else 0

@@ -104,7 +104,9 @@ class PagedKVCache:
         need(self.page_table.dtype in {torch.int32, torch.int64}, "page_table must use int32 or int64")
         need(self.sequence_lengths.dtype in {torch.int32, torch.int64}, "sequence_lengths must use int32 or int64")
         tensors = (query, self.key, self.value, self.page_table, self.sequence_lengths)
-        need(len({str(t.device) for t in tensors}) == 1, "query and paged cache metadata must share a device")
+        # A pinned host query is allowed (the kernel reads it across PCIe); everything else shares a device.
+        placed = tensors[1:] if (query.device.type == "cpu" and query.is_pinned()) else tensors
+        need(len({str(t.device) for t in placed}) == 1, "query and paged cache metadata must share a device")
         need(all(t.is_contiguous() for t in tensors), "query and paged cache tensors must be contiguous")
         if not validate_metadata:
             return
@@ -149,7 +151,7 @@ class PagedExactDecodePlan:
               **_compat: Any) -> "PagedExactDecodePlan":
         """Validate once and bind a plan.
 
-        ``splits`` asks for that many CTAs per (row, KV head); ``None`` sizes the
+        ``query`` and ``output`` may be pinned host tensors, as for ``ExactDecodePlan``.  ``splits`` asks for that many CTAs per (row, KV head); ``None`` sizes the
         grid to the GPU.  ``record_page_walk`` adds an int32 ``trace`` tensor
         shaped like the page table in which every run records the physical page
         it loaded per visited logical page.  ``dynamic_schedule`` as in
@@ -159,17 +161,18 @@ class PagedExactDecodePlan:
 
         cache.validate(query, validate_metadata=validate_metadata)
         if output is None:
-            output = torch.empty_like(query)
+            output = torch.empty(query.shape, dtype=query.dtype, device=cache.key.device)
         if output.shape != query.shape or output.dtype != query.dtype:
             raise ValueError("output must match query shape and dtype")
-        if output.device != query.device or not output.is_contiguous():
-            raise ValueError("output must be contiguous and share the query device")
+        on_cache_device = output.device == cache.key.device
+        if not (on_cache_device or (output.device.type == "cpu" and output.is_pinned())) or not output.is_contiguous():
+            raise ValueError("output must be contiguous and live on the cache device (or in pinned host memory)")
         if splits is not None and not 0 < int(splits) <= cache.max_pages_per_request:
             raise ValueError("splits must be in [1, max_pages_per_request]")
-        native.require_cuda(query, cache.key)
+        native.require_cuda(cache.key, host_io=(query, output))
         batch, _, q_heads, dim = (int(x) for x in query.shape)
         num_ctas = 0 if splits is None else int(splits) * batch * cache.kv_heads
-        workspace = native.new_workspace(query.device, batch, q_heads, cache.kv_heads, dim, num_ctas)
+        workspace = native.new_workspace(cache.key.device, batch, q_heads, cache.kv_heads, dim, num_ctas)
         trace = torch.full_like(cache.page_table, -1, dtype=torch.int32) if record_page_walk else None
         plan = native.paged_plan(query, cache.key, cache.value, cache.page_table, cache.sequence_lengths,
                                  output, workspace, layout=cache.normalized_layout, trace=trace,

@@ -183,3 +183,25 @@ def test_paged_engine_path(dev):
     assert info.stats["workspace_bytes"] == plan.direct_runner.plan.workspace_bytes
     with pytest.raises(ValueError, match="does not yet support paged KV"):
         engine.plan(q.to(dev), cache, mode="seed_only_native")
+
+
+def test_paged_plan_bound_to_pinned_host_query_and_output(dev):
+    """The paged plan, like the exact plan, may read the query from and write the result to pinned
+    host memory; the bits equal those of the plan bound to device buffers."""
+
+    g = torch.Generator().manual_seed(9)
+    batch, q_heads, kv_heads, dim, page, max_pages = 3, 8, 2, 64, 16, 8
+    num_pages = batch * max_pages
+    k = torch.randn(num_pages, kv_heads, page, dim, generator=g).bfloat16().to(dev)
+    v = torch.randn(num_pages, kv_heads, page, dim, generator=g).bfloat16().to(dev)
+    table = torch.randperm(num_pages, generator=g).to(torch.int32).view(batch, max_pages).to(dev)
+    lengths = torch.tensor([17, 128, 90], dtype=torch.int32, device=dev)
+    cache = sa.PagedKVCache(key=k, value=v, page_table=table, sequence_lengths=lengths, layout="HND")
+    q_host = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16().pin_memory()
+    out_host = torch.zeros_like(q_host).pin_memory()
+    want = sa.PagedExactDecodePlan.build(q_host.to(dev), cache, validate_metadata=False).run().cpu()
+    plan = sa.PagedExactDecodePlan.build(q_host, cache, output=out_host, validate_metadata=False)
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    assert torch.equal(out_host, want)
