@@ -55,7 +55,8 @@ size_t workspace_bytes_impl(int batch, int q_heads, int kv_heads, int head_dim, 
 {
     const int ctas = num_ctas > 0 ? std::min(num_ctas, kMaxCtas) : kMaxAutoCtas;
     const int64_t pairs = static_cast<int64_t>(batch) * q_heads;
-    const size_t a = stream_partial_floats(batch, q_heads, kv_heads, head_dim, ctas);
+    const int split = std::max(1, stream_kv_split(q_heads / kv_heads));
+    const size_t a = stream_partial_floats(batch, q_heads, kv_heads * split, head_dim, ctas);
     const size_t b = generic_partial_floats(batch, q_heads, head_dim, generic_splits_bound(pairs, num_ctas));
     return kStatusWords * 4 + counters_bytes(batch, q_heads) + round_up(std::max(a, b) * 4, 256);
 }
@@ -145,8 +146,9 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
     *why = "";
     if (p.dtype != SA_DTYPE_BF16 && p.dtype != SA_DTYPE_F16) { *why = "dtype is not bf16/fp16"; return false; }
     if (p.head_dim != 64 && p.head_dim != 128) { *why = "head_dim is not 64 or 128"; return false; }
-    const int group = p.q_heads / p.kv_heads;
-    if (group > 16) { *why = "more than 16 query heads per KV head"; return false; }
+    geo->kv_split = stream_kv_split(p.q_heads / p.kv_heads);
+    if (geo->kv_split == 0) { *why = "query heads per KV head cannot be split into groups of at most 16"; return false; }
+    const int group = p.q_heads / p.kv_heads / geo->kv_split;  // per virtual KV head
     if (p.batch > 8192) { *why = "batch larger than 8192"; return false; }
     if (stream_smem_bytes(p.head_dim, group > 8, stream_stages(p.head_dim, group > 8), p.batch) > kStreamSmemLimit) {
         *why = "batch too large for the shared-memory schedule table";
@@ -205,7 +207,7 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
         *why = "cache pointers/strides do not satisfy the TMA alignment rules";
         return false;
     }
-    const int64_t tiles = static_cast<int64_t>(p.batch) * p.kv_heads * ((max_vlen + tile - 1) / tile);
+    const int64_t tiles = static_cast<int64_t>(p.batch) * p.kv_heads * geo->kv_split * ((max_vlen + tile - 1) / tile);
     if (tiles >= (1ll << 30)) { *why = "more than 2^30 tiles"; return false; }
     int64_t ctas;
     if (p.num_ctas > 0) {
@@ -271,7 +273,7 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
     }
     size_t need;
     if (plan->use_stream) {
-        need = stream_partial_floats(p.batch, p.q_heads, p.kv_heads, p.head_dim, plan->geo.num_ctas);
+        need = stream_partial_floats(p.batch, p.q_heads, p.kv_heads * plan->geo.kv_split, p.head_dim, plan->geo.num_ctas);
     } else {
         plan->generic_splits = generic_splits(p, max_vlen);
         need = plan->generic_splits > 1

@@ -54,6 +54,7 @@ struct StreamParams {
     int tok_dim;         // TMA coordinate (1 or 2) that carries the token index
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
     int schedule;        // kScheduleBlocked / kScheduleCyclic / kScheduleClaims
+    int kv_split;        // virtual KV heads per physical KV head (kv_heads and group above are virtual)
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
@@ -738,7 +739,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             if (b != pc_b) pc_vlen = vlen_of(b);
             pc_b = b;
         }
-        f.kvh = pc_kvh;
+        f.kvh = p.kv_split > 1 ? pc_kvh / p.kv_split : pc_kvh;  // the cache's own head index
         if (lane >= p.frags_per_tile) return f;
         const unsigned vfrag = (static_cast<unsigned>(x - pc_start) << p.fpt_shift) + lane;
         const int64_t vtok0 = static_cast<int64_t>(vfrag) << p.frag_shift;
@@ -1296,6 +1297,13 @@ extern "C" __attribute__((visibility("default"))) void sa_debug_timeline(void *p
 }
 #endif
 
+int stream_kv_split(int group)
+{
+    for (int s = 1; s <= group; ++s)
+        if (group % s == 0 && group / s <= 16) return s;
+    return 0;
+}
+
 int stream_tile_tokens(int head_dim) { return kTileBytes / (head_dim * 2); }
 
 int stream_stages(int head_dim, bool rows16)
@@ -1327,8 +1335,9 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpF
     sp.trace = p.trace;
     sp.batch = p.batch;
     sp.q_heads = p.q_heads;
-    sp.kv_heads = p.kv_heads;
-    sp.group = p.q_heads / p.kv_heads;
+    sp.kv_heads = p.kv_heads * geo.kv_split;
+    sp.group = p.q_heads / sp.kv_heads;
+    sp.kv_split = geo.kv_split;
     sp.scale_log2 = kLog2e / sqrtf(static_cast<float>(p.head_dim));
     sp.frag_tokens = geo.frag_tokens;
     sp.frags_per_tile = geo.frags_per_tile;

@@ -49,9 +49,13 @@ struct StreamGeometry {
     int tok_dim;         // TMA coordinate carrying the token index (1 or 2)
     int uniform_tiles;   // tiles per row if all rows are equally long, else -1
     int num_ctas;
+    int kv_split;        // groups of more than 16 query heads: virtual KV heads per physical one (else 1)
     int schedule;        // how the CTAs of one (row, kv head) pair share its tiles (kSchedule*)
 };
 
+// Smallest s with group % s == 0 and group / s <= 16 (0 if there is none): a KV head with more
+// than 16 query heads is served as s virtual KV heads that read the same K/V rows.
+int stream_kv_split(int group);
 int stream_tile_tokens(int head_dim);
 int stream_stages(int head_dim, bool rows16);
 size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch);

@@ -25,6 +25,8 @@ def _case(rng: random.Random):
     dim = rng.choice([64, 128])
     kv_heads = rng.choice([1, 2, 4, 8])
     group = rng.choice([1, 2, 3, 4, 8] + ([16] if dim == 64 else []))
+    if rng.random() < 0.15:
+        group, kv_heads = rng.choice([24, 32, 48]), rng.choice([1, 2])   # served as 2-3 virtual KV heads of <= 16
     batch = rng.choice([1, 2, 3, 5, 8, 17, 40])
     kv_len = rng.choice([1, 7, 31, 64, 65, 300, 1000, 2049, 5000])
     layout = rng.choice(["BHND", "BNHD"])
@@ -110,3 +112,29 @@ def test_paged_stream_kernel_matches_generic_kernel_on_random_shapes(dev, seed):
     assert torch.isfinite(outs["stream"].float()).all()
     assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS, \
         (batch, kv_heads, group, dim, page, max_pages, layout, dynamic, float(diff.max()))
+
+
+@pytest.mark.parametrize("group,kv_heads,dim,layout", [(32, 1, 128, "BHND"), (48, 1, 64, "BNHD"), (24, 2, 64, "BHND"),
+                                                       (32, 2, 64, "BNHD")])
+def test_large_query_groups_run_on_the_streaming_kernel(dev, group, kv_heads, dim, layout):
+    """More than 16 query heads per KV head (multi-query models): the streaming kernel serves the
+    group as several virtual KV heads that read the same K/V rows."""
+
+    g = torch.Generator(device=dev).manual_seed(group)
+    batch, kv_len, q_heads = 3, 1500, group * kv_heads
+    q = torch.randn(batch, 1, q_heads, dim, generator=g, device=dev).bfloat16()
+    shape = (batch, kv_heads, kv_len, dim) if layout == "BHND" else (batch, kv_len, kv_heads, dim)
+    k = torch.randn(shape, generator=g, device=dev).bfloat16()
+    v = torch.randn(shape, generator=g, device=dev).bfloat16()
+    outs = {}
+    for kernel in ("stream", "generic"):
+        out = torch.full_like(q, float("nan"))
+        ws = native.new_workspace(dev, batch, q_heads, kv_heads, dim)
+        plan = native.exact_plan(q, k, v, out, ws, kv_layout=layout, kernel=kernel)
+        assert plan.kernel == (native.SA_KERNEL_STREAM if kernel == "stream" else native.SA_KERNEL_GENERIC)
+        plan.run()
+        plan.run()
+        assert native.workspace_status(ws) == 0
+        outs[kernel] = out
+    diff = (outs["stream"].float() - outs["generic"].float()).abs()
+    assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS
