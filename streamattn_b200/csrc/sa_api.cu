@@ -287,7 +287,14 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
 
 int run_plan(const sa_plan *plan, cudaStream_t stream)
 {
-    if (plan->cp.world > 0) plan->cp.step += 1;  // every rank advances in lock step, one per run
+    if (plan->cp.world > 0) {
+        // The step number travels as a launch argument: a captured launch would replay one step
+        // number for ever, and ranks would take each other's old words for new ones.
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing != cudaStreamCaptureStatusNone)
+            return fail(SA_ERR_UNSUPPORTED, "a fused context-parallel plan cannot be captured into a CUDA graph");
+        plan->cp.step += 1;  // every rank advances in lock step, one per run
+    }
     cudaError_t err = plan->use_stream ? launch_stream(plan->problem, plan->geo, plan->cp, stream)
                                        : launch_generic(plan->problem, plan->generic_splits, stream);
     if (err != cudaSuccess) return fail_cuda(err, "kernel launch failed");
