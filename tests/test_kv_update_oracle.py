@@ -66,3 +66,12 @@ def test_page_pool_allocates_lowest_first_and_recycles():
         pool.release([7])
     with pytest.raises(ValueError):
         PagePool(4, reserved=[9])
+
+
+def test_append_kv_has_no_cpu_path():
+    from streamattn_b200.kv_update import append_kv
+
+    k = torch.zeros(1, 2, 8, 64)
+    new = torch.zeros(1, 2, 1, 64)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        append_kv(k, k.clone(), new, new.clone(), torch.zeros(1, dtype=torch.int64))
