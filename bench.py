@@ -19,6 +19,16 @@ Under torchrun (N>1) every rank runs; timing is the max over ranks of CUDA-event
 time between a barrier + synchronize on both sides.  ``--impl reference`` times the
 reference's CPU PyTorch path (restated in ``oracle/torch_port.py``) on the host
 cores, on a bounded sample of the same workload.
+
+Two timings are reported for every workload.  ``value`` / ``ms_per_step`` come from the
+one region of ``--steps`` calls after ``--warmup`` calls.  ``protocol`` is independent of
+``--steps``: at least 20 warm-up calls, then 9 repeats of at least 200 calls each, every
+repeat between its own pair of CUDA events; it gives the median, minimum and maximum
+microseconds per call over the repeats (the reference times its kernels the same way,
+benchmarks/profile_paged_exact_decode.py:284-309).  At N=1 the line also carries a
+``secondary`` list with the other configurations (paged, seed-only, BNHD, decode loop and
+the 1M-token row on one GPU - the base of the strong-scaling series), each with its own
+protocol timing, roofline figures, end-to-end time and clock record.
 """
 
 from __future__ import annotations
@@ -49,13 +59,19 @@ def emit(line: dict) -> None:
 METRIC = "kv_bytes_per_second"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (None until a capture exists for the workload).
 # The reference's published number for the same metric and shape (its serving-gate artifact
 # artifacts/gate0/transposed_wgmma_exact_promoted_serving_gate_h100_20260818.json): config 2 on
 # one H100 (not a B200), 96.3 us per call = 2787 GB/s.
 PUBLISHED_GBS = {"exact_c2": 268435456 / 96.3e-6 / 1e9}
-NCU_TRAFFIC_BYTES = {"exact_c2": 272.3e6, "paged_c3": 170.9e6, "cp_c5": 8 * 541.7e6}  # cp_c5: whole row, divided by N below
+# DRAM bytes (read + write) per launch of the dominant kernel: stored results of earlier ncu
+# captures of this kernel (dram__bytes_read.sum + dram__bytes_write.sum), not measured by this run.
+NCU_TRAFFIC = {
+    "exact_c2": (272.3e6, "profiles/stream_decode_exact_c2.md"),
+    "paged_c3": (170.9e6, "profiles/stream_decode_paged_c3.md"),
+    # one eighth of the 1M-token row was captured; traffic grows in proportion to the tokens read
+    "cp_c5": (8 * 541.7e6, "profiles/stream_decode_cp_shard_d128.md"),
+    "cp_c5_1gpu": (8 * 541.7e6, "profiles/stream_decode_cp_shard_d128.md"),
+}
 
 
 def measured_hbm_peak():
@@ -80,13 +96,12 @@ class ClockSampler:
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
     QUERY = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active"
 
-    def __init__(self, index: int, period_ms: int = 100) -> None:
+    def __init__(self, index: int, period_ms: int = 50) -> None:
         self.index = index
         self.period_ms = period_ms
         self._proc = None
         self._log = None
-        self._t0 = self._t1 = None
-        self._edge_samples = []  # NVML readings taken at begin() and end() by this process
+        self._edge_samples = []  # (time, MHz, max MHz, reason bits): NVML readings taken by this process
 
     def start(self) -> "ClockSampler":
         import shutil
@@ -105,6 +120,8 @@ class ClockSampler:
         return self
 
     def _nvml_once(self) -> None:
+        import datetime
+
         try:
             import pynvml
 
@@ -112,26 +129,29 @@ class ClockSampler:
             handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             get = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
                 pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
-            self._edge_samples.append((int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+            self._edge_samples.append((datetime.datetime.now(),
+                                       int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
                                        int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)),
                                        int(get(handle))))
         except Exception:
             pass
 
-    def begin(self) -> None:
+    @staticmethod
+    def mark():
+        """A time stamp that delimits a window of samples (see :meth:`summary`)."""
+
         import datetime
 
-        self._t0 = datetime.datetime.now()
+        return datetime.datetime.now()
 
-    def sample_under_load(self) -> None:
-        """One direct NVML reading; call it while the steps just enqueued are still running."""
+    def sample_under_load(self, run=None, calls: int = 64) -> None:
+        """One direct NVML reading while ``calls`` more (untimed) calls are still running."""
 
+        if run is not None:
+            for _ in range(calls):
+                run()
         self._nvml_once()
-
-    def end(self) -> None:
-        import datetime
-
-        self._t1 = datetime.datetime.now()
+        torch.cuda.synchronize()
 
     def stop(self) -> None:
         if self._proc is not None:
@@ -142,11 +162,13 @@ class ClockSampler:
                 self._proc.kill()
             self._proc = None
 
-    def summary(self) -> dict:
+    def summary(self, t0, t1) -> dict:
+        """Median SM clock and the throttle reasons seen between the two marks."""
+
         import datetime
 
         samples, reasons, max_mhz = [], set(), None
-        if self._log is not None and self._t0 is not None and self._t1 is not None:
+        if self._log is not None:
             try:
                 self._log.flush()
                 self._log.seek(0)
@@ -160,15 +182,16 @@ class ClockSampler:
                     except ValueError:
                         continue
                     max_mhz = mx
-                    if self._t0 <= stamp <= self._t1:
+                    if t0 <= stamp <= t1:
                         samples.append(mhz)
                         reasons.update(name for bit, name in self.REASONS.items() if bits & bit)
             except Exception:
                 pass
-        for mhz, mx, bits in self._edge_samples:
-            samples.append(mhz)
-            max_mhz = mx
-            reasons.update(name for bit, name in self.REASONS.items() if bits & bit)
+        for stamp, mhz, mx, bits in self._edge_samples:
+            if t0 <= stamp <= t1:
+                samples.append(mhz)
+                max_mhz = mx
+                reasons.update(name for bit, name in self.REASONS.items() if bits & bit)
         return {
             "sm_mhz": statistics.median(samples) if samples else None,
             "sm_max_mhz": max_mhz,
@@ -191,12 +214,15 @@ SCHEDULE = {"dynamic": None}  # set from --schedule: None follows STREAMATTN_B20
 
 
 def traffic_per_launch(workload: str, world: int):
-    """DRAM read+write bytes of one launch of the dominant kernel (from the ncu captures under profiles/)."""
+    """(DRAM read+write bytes of one launch of the dominant kernel, where that figure comes from)."""
 
-    total = NCU_TRAFFIC_BYTES.get(workload)
+    total, source = NCU_TRAFFIC.get(workload, (None, None))
     if total is None:
-        return None
-    return total / world if workload == "cp_c5" else total
+        return None, None
+    source = f"stored ncu capture {source}"
+    if workload == "cp_c5":
+        return total / world, source + ", scaled by the tokens one rank reads"
+    return total, source
 
 
 def schedule_name(workload: str) -> str:
@@ -221,7 +247,7 @@ def build_exact_c2(device, layout="BHND"):
     info = dict(workload="exact_c2" if layout == "BHND" else "exact_c2_bnhd", batch=B, q_heads=Hq, kv_heads=Hkv,
                 head_dim=D, kv_len=N, kv_layout=layout, kernel=plan.kernel_name, ctas=plan.num_ctas,
                 bytes=2 * B * Hkv * N * D * 2, launches=plan.launches_per_run)
-    return plan.run, q, plan.output, info, plan
+    return {"run": plan.run, "q": q, "out": plan.output, "info": info, "plan": plan}
 
 
 def build_paged_c3(device):
@@ -246,7 +272,7 @@ def build_paged_c3(device):
     info = dict(workload="paged_c3", batch=B, q_heads=Hq, kv_heads=Hkv, head_dim=D, page_size=page, capacity=cap,
                 total_tokens=tokens, kernel=plan.kernel_name, ctas=plan.num_ctas,
                 bytes=2 * Hkv * D * 2 * tokens + 4 * pages, launches=plan.launches_per_run)
-    return plan.run, q, plan.output, info, plan
+    return {"run": plan.run, "q": q, "out": plan.output, "info": info, "plan": plan}
 
 
 def build_loop_c2(device):
@@ -287,7 +313,7 @@ def build_loop_c2(device):
                 kv_len="grows by one per step from %d (bytes counted at the mean length %d)" % (start, mean_len),
                 kv_layout="BHND", kernel=plan.kernel_name + " after append_kv_kernel", ctas=plan.num_ctas,
                 bytes=2 * B * Hkv * mean_len * D * 2, launches=plan.launches_per_run + 1)
-    return run, q_raw, plan.output, info, plan
+    return {"run": run, "q": q_raw, "out": plan.output, "info": info, "plan": plan}
 
 
 def build_seed_c4(device):
@@ -302,12 +328,17 @@ def build_seed_c4(device):
     middle = (torch.randperm(2032 - 4, generator=g)[:4] + 4).tolist()
     blocks = [0, 1, 2, 3, *middle, *range(2032, 2048)]
     out = torch.empty_like(q)
-    ws = native.new_workspace(device, B, Hq, Hkv, D)
-    plan = native.seed_plan(q, k, v, out, ws, block_size=bs, blocks=blocks)
+
+    def bind(q_buf, out_buf):
+        return native.seed_plan(q_buf, k, v, out_buf, native.new_workspace(device, B, Hq, Hkv, D), block_size=bs,
+                                blocks=blocks)
+
+    plan = bind(q, out)
     info = dict(workload="seed_c4", batch=B, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, seed_tokens=384,
                 kernel=plan.kernel_name, ctas=plan.num_ctas, bytes=2 * B * Hkv * 384 * D * 2,
-                launches=plan.launches, l2="seed set (3 MB) stays L2-resident between calls")
-    return plan.run, q, out, info, plan
+                launches=plan.launches,
+                l2="seed set (3 MB) stays L2-resident between back-to-back calls; cold_l2 gives the HBM case")
+    return {"run": plan.run, "q": q, "out": out, "info": info, "plan": plan, "rebind": bind}
 
 
 def build_cp_c5(device, rank, world, exchange="auto", kv_len=1048576):
@@ -327,12 +358,15 @@ def build_cp_c5(device, rank, world, exchange="auto", kv_len=1048576):
         k[:, :, a - lo:b - lo] = kc[:, :, a - c0:b - c0]
         v[:, :, a - lo:b - lo] = vc[:, :, a - c0:b - c0]
         del kc, vc
-    cp = ContextParallelExactDecode(q, k, v, kv_layout="BHND", exchange=exchange)
+    def bind(q_buf, out_buf):
+        return ContextParallelExactDecode(q_buf, k, v, kv_layout="BHND", exchange=exchange, output=out_buf)
+
+    cp = bind(q, None)
     info = dict(workload="cp_c5", batch=1, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, shard_tokens=hi - lo,
                 kernel=cp.kernel_name, ctas=cp._plan.num_ctas, bytes=2 * Hkv * N * D * 2,
                 exchange_bytes_per_rank=cp.exchange_bytes_per_rank, exchange=cp.exchange,
                 launches=cp.launches_per_run, parallelism=f"cp{world}")
-    return cp.run, q, cp.output, info, cp
+    return {"run": cp.run, "q": q, "out": cp.output, "info": info, "plan": cp, "rebind": bind}
 
 
 def time_region(fn, steps, device):
@@ -344,6 +378,185 @@ def time_region(fn, steps, device):
     stop.record()
     torch.cuda.synchronize(device)
     return start.elapsed_time(stop) * 1e-3
+
+
+class Ranks:
+    """Barrier and max-over-ranks for one process per GPU (no-ops in a single process)."""
+
+    def __init__(self, device, world: int, distributed: bool) -> None:
+        self.device, self.world, self.distributed = device, world, distributed
+
+    def barrier(self) -> None:
+        if self.distributed:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize(self.device)
+
+    def max_over_ranks(self, values):
+        if not self.distributed or self.world == 1:
+            return list(values)
+        import torch.distributed as dist
+
+        t = torch.tensor(list(values), dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+
+PROTOCOL_WARMUP = 20
+PROTOCOL_ITERS = 200
+PROTOCOL_REPEATS = 9
+
+
+def protocol_time(fn, ranks: Ranks, *, warmup: int = PROTOCOL_WARMUP, min_iters: int = PROTOCOL_ITERS,
+                  repeats: int = PROTOCOL_REPEATS, min_repeat_s: float = 0.05) -> dict:
+    """Median / min / max microseconds per call over ``repeats`` regions of at least ``min_iters`` calls.
+
+    Every region sits between its own pair of CUDA events after a barrier + synchronize, and its
+    time is the maximum over the ranks.  A region lasts at least ``min_repeat_s`` (more calls for
+    short kernels) so that the clock sampler, which reads every 50 ms, sees the GPU under this
+    very load several times per workload.
+    """
+
+    for _ in range(max(0, warmup - 10)):
+        fn()
+    ranks.barrier()
+    probe = ranks.max_over_ranks([time_region(fn, 10, ranks.device) / 10])[0]  # the last 10 warm-up calls, timed
+    iters = max(min_iters, int(min_repeat_s / max(probe, 1e-7)) + 1)
+    times = []
+    for _ in range(repeats):
+        ranks.barrier()
+        times.append(time_region(fn, iters, ranks.device) / iters * 1e6)
+    ranks.barrier()
+    times = ranks.max_over_ranks(times)
+    return {"us_per_call": statistics.median(times), "min_us": min(times), "max_us": max(times),
+            "repeats": repeats, "iters_per_repeat": iters, "warmup": max(warmup, 10)}
+
+
+def flush_l2(device, scratch: dict) -> None:
+    """Overwrite a buffer larger than the 126 MB L2 so that the next call starts from HBM."""
+
+    if "buf" not in scratch:
+        scratch["buf"] = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    scratch["buf"].add_(1)
+
+
+def cold_time(fn, device, calls: int = 40) -> dict:
+    """Microseconds per call with L2 flushed (outside the timed events) before every call."""
+
+    scratch, times = {}, []
+    for i in range(calls + 3):
+        flush_l2(device, scratch)
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize(device)
+        if i >= 3:
+            times.append(start.elapsed_time(stop) * 1e3)
+    return {"us_per_call": statistics.median(times), "min_us": min(times), "max_us": max(times), "calls": calls,
+            "note": "single calls, 256 MB written between calls so K/V come from HBM; event pair per call"}
+
+
+def make_e2e(workload: str, case, device):
+    """The end-to-end step of a workload: host query in, result in host memory, waited for.
+
+    Returns (step, mode text, pinned host query, pinned host output).  Plans that can bind pinned
+    host buffers do so (the kernel reads q and writes the result across PCIe itself: one launch
+    and one wait per step); the others enqueue two async copies around ``run()``.
+    """
+
+    import streamattn_b200 as sa
+
+    run, q_dev, out_dev, plan = case["run"], case["q"], case["out"], case["plan"]
+    stream = torch.cuda.current_stream(device)  # looked up once: the step itself stays minimal
+    q_host = q_dev.cpu().pin_memory()
+    out_host = torch.empty(out_dev.shape, dtype=out_dev.dtype).pin_memory()
+    bound = "plan bound to pinned host query/output: the kernel reads q and writes out over PCIe"
+    host_run = None
+    if workload in ("exact_c2", "exact_c2_bnhd", "cp_c5_1gpu"):
+        host_run = sa.ExactDecodePlan.build(q_host, plan.key_cache, plan.value_cache, output=out_host,
+                                            kv_layout=plan.kv_layout, dynamic_schedule=SCHEDULE["dynamic"]).run
+    elif workload == "paged_c3":
+        host_run = sa.PagedExactDecodePlan.build(q_host, plan.cache, output=out_host, validate_metadata=False,
+                                                 dynamic_schedule=SCHEDULE["dynamic"]).run
+    elif workload == "seed_c4":
+        host_run = case["rebind"](q_host, out_host).run
+    elif workload == "cp_c5":
+        host_run = case["rebind"](q_host, out_host).run
+    if host_run is not None:
+        def step():
+            host_run()
+            stream.synchronize()
+
+        return step, bound, q_host, out_host
+
+    def step():  # noqa: F811
+        q_dev.copy_(q_host, non_blocking=True)
+        run()
+        out_host.copy_(out_dev, non_blocking=True)
+        stream.synchronize()
+
+    return step, "pinned-host query copied in, output copied out (two async copies around run())", q_host, out_host
+
+
+def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, steps: int, warmup: int,
+                 headline: bool) -> dict:
+    """All figures of one workload: --steps region (headline only), protocol timing, e2e, roofline, clocks."""
+
+    device, world = ranks.device, ranks.world
+    run, info = case["run"], dict(case["info"])
+    alg_bytes = info.pop("bytes")
+    launches = info.pop("launches")
+    per_gpu_bytes = alg_bytes / world if workload == "cp_c5" else alg_bytes
+    peak, peak_kind = measured_hbm_peak()
+    result = {"workload": workload}
+
+    t_begin = clocks.mark()
+    if headline:
+        for _ in range(warmup):
+            run()
+        ranks.barrier()
+        elapsed = time_region(run, steps, device)
+        ranks.barrier()
+        result["step_s"] = ranks.max_over_ranks([elapsed])[0] / steps
+    proto = protocol_time(run, ranks)
+    clocks.sample_under_load(run)
+    t_end = clocks.mark()
+    result["protocol"] = proto
+
+    e2e_step, e2e_mode, q_host, out_host = make_e2e(workload, case, device)
+    e2e = protocol_time(e2e_step, ranks, warmup=10, min_iters=50, min_repeat_s=0.0)
+    if workload != "loop_c2":  # the loop's cache grows between the two runs
+        run()
+        torch.cuda.synchronize(device)
+        torch.testing.assert_close(out_host.float(), case["out"].float().cpu(), atol=2e-2, rtol=0)
+    us = proto["us_per_call"]
+    achieved = per_gpu_bytes / (us * 1e-6) / 1e9
+    traffic, traffic_source = traffic_per_launch(workload, world)
+    result.update({
+        "us_per_call": us, "min_us": proto["min_us"], "max_us": proto["max_us"],
+        "gb_per_s": alg_bytes / (us * 1e-6) / 1e9,
+        "config": {**info, "schedule": schedule_name(workload),
+                   "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2")},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "traffic_source": traffic_source,
+                     "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "kernel": info["kernel"], "algorithmic_bytes_per_launch": per_gpu_bytes,
+                     "timed": "median of the protocol repeats"},
+        "e2e": {"value": alg_bytes / (e2e["us_per_call"] * 1e-6) / 1e9, "unit": UNIT,
+                "us_per_call": e2e["us_per_call"], "min_us": e2e["min_us"], "max_us": e2e["max_us"],
+                "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
+                "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
+                "note": e2e_mode + "; the KV cache is resident device state bound to the plan"},
+        "launches_per_call": launches,
+        "clock_window": (t_begin, t_end),
+        "device_status": case["plan"].device_status() if hasattr(case["plan"], "device_status") else 0,
+    })
+    if workload == "seed_c4":
+        result["cold_l2"] = cold_time(run, device)
+    return result
 
 
 def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1, budget_s: float = 30.0) -> dict:
@@ -397,6 +610,39 @@ def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1, budget_s
             "ms_per_sample": dt * 1e3, "samples_timed": done}
 
 
+BUILDERS = {
+    "exact_c2": lambda device: build_exact_c2(device),
+    "exact_c2_bnhd": lambda device: build_exact_c2(device, "BNHD"),
+    "paged_c3": build_paged_c3,
+    "seed_c4": build_seed_c4,
+    "loop_c2": build_loop_c2,
+    "cp_c5_1gpu": lambda device: build_cp_c5_single(device),
+}
+SECONDARY = ("paged_c3", "seed_c4", "exact_c2_bnhd", "loop_c2", "cp_c5_1gpu")
+
+
+def cp_oracle_check(device, out_dev, kv_head: int = 0) -> float:
+    """Max |difference| between the context-parallel result and the CPU oracle on one KV group.
+
+    The oracle (C, double accumulation) is run on the same seeded values for the query heads of
+    ``kv_head`` over the whole 1M-token row; it is the checker here, outside every timed region.
+    """
+
+    from oracle import cpu_oracle
+
+    Hq, Hkv, D, N, chunk = 32, 8, 128, 1048576, 65536
+    group = Hq // Hkv
+    q = _randn_bf16((1, 1, Hq, D), 100, device)[:, :, kv_head * group:(kv_head + 1) * group].float().cpu()
+    k = torch.empty(1, 1, N, D, dtype=torch.float32)
+    v = torch.empty_like(k)
+    for c0 in range(0, N, chunk):
+        k[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1000 + 2 * (c0 // chunk), device)[:, kv_head:kv_head + 1].float().cpu()
+        v[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1001 + 2 * (c0 // chunk), device)[:, kv_head:kv_head + 1].float().cpu()
+    want = cpu_oracle.exact_decode(q, k, v, kv_layout="BHND")
+    got = out_dev[:, :, kv_head * group:(kv_head + 1) * group].float().cpu()
+    return float((got - want).abs().max())
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,8 +650,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
-                    choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "loop_c2", "cp_c5"])
+                    choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "loop_c2", "cp_c5",
+                             "cp_c5_1gpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="N=1: only the headline workload (the other configurations are skipped)")
+    ap.add_argument("--no-oracle-check", action="store_true",
+                    help="cp_c5: skip the CPU-oracle comparison of one KV group (about 10 s on rank 0)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "peer", "nccl"],
                     help="cp_c5 only: how the per-rank states meet (fused peer-store kernel or NCCL all-gather)")
     ap.add_argument("--schedule", default="default", choices=["default", "static", "dynamic"],
@@ -437,7 +688,8 @@ def main() -> None:
             "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": base["samples_timed"], "steps_requested": args.steps, "warmup": min(warmup, 3),
             "ms_per_step": base["ms_per_sample"],
-            "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if workload.startswith("cp_c5") else "weak",
+            "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": workload, "sample": base["sample"]},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -451,198 +703,135 @@ def main() -> None:
     torch.cuda.set_device(device)
     clocks = ClockSampler(local_rank).start()  # child process: it comes up while the inputs are built
     distributed = world > 1
-    if distributed:
+    if distributed or workload == "cp_c5":
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=device)
-    elif workload == "cp_c5":
-        import torch.distributed as dist
-
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29555")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        if not distributed:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29555")
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        else:
+            dist.init_process_group("nccl", device_id=device)
         distributed = True
+    ranks = Ranks(device, world, distributed)
 
-    if workload == "exact_c2":
-        run, q_dev, out_dev, info, plan = build_exact_c2(device)
-    elif workload == "exact_c2_bnhd":
-        run, q_dev, out_dev, info, plan = build_exact_c2(device, "BNHD")
-    elif workload == "paged_c3":
-        run, q_dev, out_dev, info, plan = build_paged_c3(device)
-    elif workload == "seed_c4":
-        run, q_dev, out_dev, info, plan = build_seed_c4(device)
-    elif workload == "loop_c2":
-        run, q_dev, out_dev, info, plan = build_loop_c2(device)
-    else:
-        run, q_dev, out_dev, info, plan = build_cp_c5(device, rank, world, args.exchange, args.cp_kv_len)
-    alg_bytes = info.pop("bytes")
-    launches = info.pop("launches")
+    def build(name):
+        if name == "cp_c5":
+            return build_cp_c5(device, rank, world, args.exchange, args.cp_kv_len)
+        return BUILDERS[name](device)
 
-    def barrier():
-        if distributed:
-            import torch.distributed as dist
-
-            dist.barrier()
-        torch.cuda.synchronize(device)
-
-    def max_over_ranks(x: float) -> float:
-        if not distributed or world == 1:
-            return x
-        import torch.distributed as dist
-
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- kernel-resident timing: inputs already in HBM ----
-    for _ in range(warmup):
-        run()
-    barrier()
-    clocks.begin()
-    elapsed = time_region(run, args.steps, device)
-    barrier()
-    elapsed = max_over_ranks(elapsed)
-    if not args.profile:
-        # Short regions: keep the same step running (untimed) so that the 100 ms sampler sees the
-        # GPU under this very load a few times.  Every rank runs the same number of extra steps
-        # (the count follows from the agreed time), as lock-stepped ranks must.
-        extra = int(max(0.0, 0.6 - elapsed) / (elapsed / args.steps))
-        for _ in range(extra):
-            run()
-        clocks.sample_under_load()
-        torch.cuda.synchronize(device)
-    clocks.end()
-    clocks.stop()
-    barrier()
-    step_s = elapsed / args.steps
+    case = build(workload)
 
     if args.profile:
+        for _ in range(warmup):
+            case["run"]()
+        ranks.barrier()
+        step_s = ranks.max_over_ranks([time_region(case["run"], args.steps, device)])[0] / args.steps
         if rank == 0:
             emit({"profile_run": True, "workload": workload, "us_per_call": step_s * 1e6})
+        clocks.stop()
         if distributed:
-            import torch.distributed as dist
-
             dist.destroy_process_group()
         return
 
-    # ---- end to end through the public plan API with host buffers ----
-    # Every step: the query comes from pinned host memory, the result ends in pinned host memory
-    # and is waited for.  Default path: async copy in, plan.run(), async copy out, stream sync.
-    e2e_stream = torch.cuda.current_stream(device)  # looked up once: the step itself stays minimal
-    q_host = q_dev.cpu().pin_memory()
-    out_host = torch.empty(out_dev.shape, dtype=out_dev.dtype).pin_memory()
+    head = measure_case(workload, case, ranks, clocks, steps=args.steps, warmup=warmup, headline=True)
+    step_s = head.pop("step_s")
+    alg_bytes = case["info"]["bytes"]
+    launches = case["info"]["launches"]
 
-    def e2e_step():
-        q_dev.copy_(q_host, non_blocking=True)
-        run()
-        out_host.copy_(out_dev, non_blocking=True)
-        e2e_stream.synchronize()
-
-    e2e_mode = "pinned-host query copied in, output copied out (two async copies around plan.run())"
-    if workload in ("exact_c2", "exact_c2_bnhd"):
-        # The exact plan can bind pinned host buffers directly: the kernel reads the query and
-        # writes the output across PCIe itself, so a step is one launch plus the wait.
-        import streamattn_b200 as sa
-
-        host_plan = sa.ExactDecodePlan.build(q_host, plan.key_cache, plan.value_cache, output=out_host,
-                                             kv_layout=plan.kv_layout)
-
-        def e2e_step():  # noqa: F811
-            host_plan.run()
-            e2e_stream.synchronize()
-
-        e2e_mode = "plan bound to pinned host query/output: the kernel reads q and writes out over PCIe"
-    elif workload == "paged_c3":
-        import streamattn_b200 as sa
-
-        host_plan = sa.PagedExactDecodePlan.build(q_host, plan.cache, output=out_host, validate_metadata=False,
-                                                  dynamic_schedule=SCHEDULE["dynamic"])
-
-        def e2e_step():  # noqa: F811
-            host_plan.run()
-            e2e_stream.synchronize()
-
-        e2e_mode = "plan bound to pinned host query/output: the kernel reads q and writes out over PCIe"
-
-    for _ in range(warmup):
-        e2e_step()
-    barrier()
-    e2e_steps = max(10, args.steps // 4)
-    e2e_elapsed = max_over_ranks(time_region(e2e_step, e2e_steps, device))
-    barrier()
-    e2e_s = e2e_elapsed / e2e_steps
-    if workload in ("exact_c2", "exact_c2_bnhd", "paged_c3"):
-        torch.testing.assert_close(out_host.float(), out_dev.float().cpu(), atol=2e-2, rtol=0)
-
-    status = plan.device_status() if hasattr(plan, "device_status") else 0
-    peak, peak_kind = measured_hbm_peak()
-    per_gpu_bytes = alg_bytes / world if workload == "cp_c5" else alg_bytes
-    achieved = per_gpu_bytes / step_s / 1e9
-
-    local_kernel_us = None
+    extra = {}
     if workload == "cp_c5":
+        plan = case["plan"]
         # The shard kernel alone (no exchange): what the exchange + rank skew add is the difference.
-        for _ in range(3):
-            plan.run_local()
-        barrier()
-        local_kernel_us = max_over_ranks(time_region(plan.run_local, 100, device)) / 100 * 1e6
-        barrier()
+        extra["cp_local_kernel_us"] = protocol_time(plan.run_local, ranks, repeats=5, min_repeat_s=0.0)["us_per_call"]
+        if world > 1:
+            # Every rank holds the merged result: the copies must be bit-identical.
+            case["run"]()
+            torch.cuda.synchronize(device)
+            mine = case["out"].contiguous().view(torch.int16).to(torch.int32)
+            low, high = mine.clone(), mine.clone()
+            dist.all_reduce(low, op=dist.ReduceOp.MIN)
+            dist.all_reduce(high, op=dist.ReduceOp.MAX)
+            extra["cp_ranks_identical"] = bool(torch.equal(low, high))
+            if rank == 0:
+                # One-GPU time of the same 1M-token row, measured in this run on rank 0: the base of
+                # the strong-scaling series.
+                full = build_cp_c5_single(device)
+                single = protocol_time(full["run"], Ranks(device, 1, False), repeats=5, min_iters=20,
+                                       min_repeat_s=0.0)
+                extra["cp_single_gpu_us"] = single["us_per_call"]
+                cp_max_abs = float((full["run"]().float() - case["out"].float()).abs().max())
+                assert cp_max_abs <= 2e-2, f"context-parallel result differs from the one-GPU result by {cp_max_abs}"
+                extra["cp_max_abs_vs_1gpu"] = cp_max_abs
+                extra["cp_speedup_vs_1gpu"] = single["us_per_call"] / head["us_per_call"]
+                extra["strong_scaling_efficiency"] = single["us_per_call"] / (world * head["us_per_call"])
+                extra["strong_scaling_note"] = ("cp_single_gpu_us / (n_gpus * us_per_call): the same 1M-token row on "
+                                                "one GPU, timed on rank 0 in this run, against the protocol median "
+                                                "of the sharded step")
+                del full
+                torch.cuda.empty_cache()
+        if rank == 0 and not args.no_oracle_check and args.cp_kv_len == 1048576:
+            diff = cp_oracle_check(device, case["out"])
+            assert diff <= 2e-2, f"context-parallel result differs from the CPU oracle by {diff}"
+            extra["cp_max_abs_vs_oracle"] = diff
+            extra["cp_oracle_heads"] = "query heads 0-3 (KV head 0), all 1,048,576 tokens, C oracle in double"
+        ranks.barrier()
 
-    single_gpu_us = None
-    cp_max_abs = None
-    if workload == "cp_c5" and world > 1 and rank == 0:
-        # One-GPU time of the same 1M-token row, measured in this run on rank 0 (not in the timed region).
-        full = build_cp_c5_single(device)
-        for _ in range(3):
-            full()
-        single_gpu_us = time_region(full, 10, device) / 10 * 1e6
-        # Same values on one GPU: the sharded result must agree within the bf16 output tolerance.
-        cp_max_abs = float((full().float() - out_dev.float()).abs().max())
-        assert cp_max_abs <= 2e-2, f"context-parallel result differs from the one-GPU result by {cp_max_abs}"
-    if distributed:
-        barrier()
+    secondary = []
+    if world == 1 and workload == "exact_c2" and not args.no_secondary:
+        del case
+        torch.cuda.empty_cache()
+        for name in SECONDARY:
+            other = build(name)
+            entry = measure_case(name, other, ranks, clocks, steps=args.steps, warmup=warmup, headline=False)
+            secondary.append(entry)
+            del other
+            torch.cuda.empty_cache()
+    clocks.stop()
+    for entry in [head, *secondary]:
+        entry["clocks"] = clocks.summary(*entry.pop("clock_window"))
 
     if rank == 0:
+        value = alg_bytes / step_s / 1e9
+        roofline = dict(head["roofline"])
+        # The line's roofline follows the --steps region, like ``value``; the protocol median is beside it.
+        per_gpu_bytes = roofline["algorithmic_bytes_per_launch"]
+        roofline["achieved"] = per_gpu_bytes / step_s / 1e9
+        roofline["frac"] = roofline["achieved"] / roofline["peak"]
+        roofline["frac_of_nominal_8tbs"] = roofline["achieved"] / 8000.0
+        roofline["timed"] = "the --steps region; protocol.roofline_frac is the median-of-repeats figure"
         line = {
-            "metric": METRIC, "value": alg_bytes / step_s / 1e9, "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": step_s * 1e3, "us_per_call": step_s * 1e6,
-            "higher_is_better": True, "scaling": "strong" if workload == "cp_c5" else "weak",
-            "vs_baseline": (alg_bytes / step_s / 1e9) / PUBLISHED_GBS[workload] if workload in PUBLISHED_GBS else None,
+            "higher_is_better": True, "scaling": "strong" if workload.startswith("cp_c5") else "weak",
+            "vs_baseline": value / PUBLISHED_GBS[workload] if workload in PUBLISHED_GBS else None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {**info, "schedule": schedule_name(workload),
+            "config": {**head["config"],
                        **({"vs_baseline_is": "the reference's published 96.3 us on one H100 for this shape"}
                           if workload in PUBLISHED_GBS else {}),
-                       "l2_hygiene": info.get("l2", "inputs larger than the 126 MB L2"),
                        "timing": "CUDA events around K back-to-back calls, max over ranks"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic_per_launch(workload, world),
-                         "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8tbs": achieved / 8000.0,
-                         "kernel": info["kernel"], "algorithmic_bytes_per_launch": per_gpu_bytes},
-            "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": UNIT, "us_per_call": e2e_s * 1e6,
-                    "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
-                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
-                    "note": e2e_mode + "; the KV cache is resident device state bound to the plan"},
+            "roofline": roofline,
+            "protocol": {**head["protocol"], "gb_per_s": head["gb_per_s"],
+                         "roofline_frac": head["roofline"]["frac"],
+                         "how": "median of 9 repeats, each >= 200 calls between one pair of CUDA events, after "
+                                ">= 20 warm-up calls; max over ranks per repeat"},
+            "e2e": head["e2e"],
             "gpu_launches": args.steps * launches,
-            "clocks": clocks.summary(),
-            "device_status": status,
+            "clocks": head["clocks"],
+            "device_status": head["device_status"],
+            **extra,
         }
-        if local_kernel_us is not None:
-            line["cp_local_kernel_us"] = local_kernel_us
-        if single_gpu_us is not None:
-            line["cp_single_gpu_us"] = single_gpu_us
-            line["cp_max_abs_vs_1gpu"] = cp_max_abs
-            line["cp_speedup_vs_1gpu"] = single_gpu_us / (step_s * 1e6)
+        if secondary:
+            line["secondary"] = secondary
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline_sample(workload)
+            line["cpu_baseline"] = cpu_baseline_sample("cp_c5" if workload == "cp_c5_1gpu" else workload)
         emit(line)
     if distributed:
-        import torch.distributed as dist
-
         dist.destroy_process_group()
 
 
 def build_cp_c5_single(device):
-    """The whole 1M-token config-5 row on one GPU (local kernel + merge, no collective)."""
+    """The whole 1M-token config-5 row on one GPU (one launch, no exchange): the strong-scaling base."""
 
     import streamattn_b200 as sa
 
@@ -655,7 +844,10 @@ def build_cp_c5_single(device):
         k[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1000 + 2 * (c0 // chunk), device)
         v[:, :, c0:c0 + chunk] = _randn_bf16((1, Hkv, chunk, D), 1001 + 2 * (c0 // chunk), device)
     plan = sa.ExactDecodePlan.build(q, k, v, kv_layout="BHND")
-    return plan.run
+    info = dict(workload="cp_c5_1gpu", batch=1, q_heads=Hq, kv_heads=Hkv, head_dim=D, kv_len=N, kv_layout="BHND",
+                kernel=plan.kernel_name, ctas=plan.num_ctas, bytes=2 * Hkv * N * D * 2,
+                launches=plan.launches_per_run)
+    return {"run": plan.run, "q": q, "out": plan.output, "info": info, "plan": plan}
 
 
 if __name__ == "__main__":

@@ -80,7 +80,10 @@ class ContextParallelExactDecode:
     """Exact decode over a KV sequence sharded across the ranks of a process group.
 
     Bound once to this rank's shard; ``run()`` launches the local kernel and the
-    exchange + merge on the current stream and allocates nothing.
+    exchange + merge on the current stream and allocates nothing.  ``query`` and
+    ``output`` may be pinned host tensors: the kernels then read the query and
+    write the merged result across PCIe themselves, so a host-driven step is one
+    launch and one wait with no separate copies.
     ``key_shard`` / ``value_shard`` hold this rank's tokens only, in ``kv_layout``
     (``"BHND"`` head-major by default).  ``shard_lens`` optionally gives per-row
     valid token counts inside the shard (ragged rows).  ``exchange`` selects how
@@ -98,16 +101,16 @@ class ContextParallelExactDecode:
             raise RuntimeError("torch.distributed must be initialised for context-parallel decode")
         if exchange not in ("auto", "fused", "peer", "nccl"):
             raise ValueError("exchange must be auto, fused, peer or nccl")
-        native.require_cuda(query, key_shard, value_shard)
+        device = native.require_cuda(key_shard, value_shard, host_io=(query, output))
         self.group = group
         self.world_size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.query = query
         batch, _, q_heads, dim = (int(x) for x in query.shape)
         kv_heads = int(key_shard.shape[1] if kv_layout == "BHND" else key_shard.shape[2])
-        self.output = torch.empty_like(query) if output is None else output
-        self.local_state = torch.empty(batch, q_heads, dim + 2, dtype=torch.float32, device=query.device)
-        self.workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
+        self.output = torch.empty(query.shape, dtype=query.dtype, device=device) if output is None else output
+        self.local_state = torch.empty(batch, q_heads, dim + 2, dtype=torch.float32, device=device)
+        self.workspace = native.new_workspace(device, batch, q_heads, kv_heads, dim, num_ctas)
         self._plan = native.exact_plan(query, key_shard, value_shard, self.local_state, self.workspace,
                                        kv_layout=kv_layout, seq_lens=shard_lens, out_state=True,
                                        num_ctas=num_ctas, kernel=kernel)
@@ -123,7 +126,7 @@ class ContextParallelExactDecode:
 
             if self.world_size == 1:
                 return ok
-            flag = torch.tensor([1 if ok else 0], device=query.device)
+            flag = torch.tensor([1 if ok else 0], device=device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
             return bool(int(flag.item()))
 
@@ -145,14 +148,14 @@ class ContextParallelExactDecode:
             if shard_lens is not None:
                 raise ValueError("the fused exchange needs a uniform shard length")
             nbytes = native.cp_fused_bytes(self.world_size, batch, q_heads, kv_heads, dim)
-            keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
+            keep, ptrs = _peer_exchange_buffers(nbytes, device, group)
             self._fused = native.cp_fused_plan(query, key_shard, value_shard, self.output, self.workspace, ptrs,
                                                self.rank, kv_layout=kv_layout, num_ctas=num_ctas)
             self._keepalive = keep
 
         def build_peer() -> None:
             nbytes = native.cp_exchange_bytes(self.world_size, self._rows, dim)
-            keep, ptrs = _peer_exchange_buffers(nbytes, query.device, group)
+            keep, ptrs = _peer_exchange_buffers(nbytes, device, group)
             self._peer = native.PeerExchange(self.local_state, ptrs, self.rank, self.output)
             self._keepalive = keep
 
@@ -163,7 +166,7 @@ class ContextParallelExactDecode:
             self.exchange = "peer"
         if self.exchange == "nccl":
             self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
-                                        device=query.device)
+                                        device=device)
 
     @property
     def kernel_name(self) -> str:

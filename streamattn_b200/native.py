@@ -420,7 +420,7 @@ def paged_plan(query: torch.Tensor, key_pages: torch.Tensor, value_pages: torch.
 def seed_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
               workspace: torch.Tensor, *, block_size: int, blocks: Sequence[int],
               kv_layout: str = "BNHD", num_ctas: int = 0, kernel: str = "auto") -> NativePlan:
-    device = require_cuda(query, key, value, output, workspace)
+    device = require_cuda(key, value, workspace, host_io=(query, output))
     if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
         raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
     q_sb, q_sh = _q_strides(query)
@@ -443,7 +443,7 @@ def seed_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, outpu
 def merge_states(states: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
     """states [parts, rows, D+2] float32 -> output [rows, D] (any supported dtype)."""
 
-    device = require_cuda(states, output)
+    device = require_cuda(states, host_io=(output,))
     if states.dtype != torch.float32 or states.dim() != 3 or not states.is_contiguous():
         raise ValueError("states must be a contiguous float32 [parts, rows, dim + 2] tensor")
     parts, rows, width = map(int, states.shape)
@@ -469,7 +469,7 @@ class PeerExchange:
 
     def __init__(self, local_state: torch.Tensor, peer_buffer_ptrs: Sequence[int], rank: int,
                  output: torch.Tensor) -> None:
-        device = require_cuda(local_state, output)
+        device = require_cuda(local_state, host_io=(output,))
         if local_state.dtype != torch.float32 or local_state.dim() != 3 or not local_state.is_contiguous():
             raise ValueError("local_state must be a contiguous float32 [batch, heads, dim + 2] tensor")
         self.world = len(peer_buffer_ptrs)
@@ -512,9 +512,12 @@ def cp_fused_bytes(world_size: int, batch: int, q_heads: int, kv_heads: int, hea
 def cp_fused_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
                   workspace: torch.Tensor, peer_buffer_ptrs: Sequence[int], rank: int, *,
                   kv_layout: str = "BHND", num_ctas: int = 0) -> NativePlan:
-    """One-launch context-parallel step: shard decode + peer exchange + cross-rank merge."""
+    """One-launch context-parallel step: shard decode + peer exchange + cross-rank merge.
 
-    device = require_cuda(query, key, value, output, workspace)
+    ``query`` and ``output`` may be pinned host tensors, as in :func:`exact_plan`.
+    """
+
+    device = require_cuda(key, value, workspace, host_io=(query, output))
     if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
         raise ValueError("query/key/value must share a dtype of bf16 or fp16")
     q_sb, q_sh = _q_strides(query)
