@@ -96,7 +96,7 @@ class ClockSampler:
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
     QUERY = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active"
 
-    def __init__(self, index: int, period_ms: int = 50) -> None:
+    def __init__(self, index: int, period_ms: int = 25) -> None:
         self.index = index
         self.period_ms = period_ms
         self._proc = None
@@ -409,13 +409,12 @@ PROTOCOL_REPEATS = 9
 
 
 def protocol_time(fn, ranks: Ranks, *, warmup: int = PROTOCOL_WARMUP, min_iters: int = PROTOCOL_ITERS,
-                  repeats: int = PROTOCOL_REPEATS, min_repeat_s: float = 0.05) -> dict:
+                  repeats: int = PROTOCOL_REPEATS, min_repeat_s: float = 0.0) -> dict:
     """Median / min / max microseconds per call over ``repeats`` regions of at least ``min_iters`` calls.
 
     Every region sits between its own pair of CUDA events after a barrier + synchronize, and its
-    time is the maximum over the ranks.  A region lasts at least ``min_repeat_s`` (more calls for
-    short kernels) so that the clock sampler, which reads every 50 ms, sees the GPU under this
-    very load several times per workload.
+    time is the maximum over the ranks.  ``min_repeat_s`` > 0 lengthens the regions of short
+    kernels (more calls per region).
     """
 
     for _ in range(max(0, warmup - 10)):
@@ -522,7 +521,10 @@ def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, ste
         ranks.barrier()
         result["step_s"] = ranks.max_over_ranks([elapsed])[0] / steps
     proto = protocol_time(run, ranks)
-    clocks.sample_under_load(run)
+    # Keep the same call running (untimed) for a moment so that the clock sampler, which reads
+    # every 25 ms, sees the GPU under this very load; every rank runs the same number of calls.
+    extra = int(min(0.15 / max(proto["us_per_call"] * 1e-6, 1e-7), 20000))
+    clocks.sample_under_load(run, calls=extra)
     t_end = clocks.mark()
     result["protocol"] = proto
 

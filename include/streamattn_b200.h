@@ -62,7 +62,10 @@ enum sa_kernel_choice { SA_KERNEL_AUTO = 0, SA_KERNEL_STREAM = 1, SA_KERNEL_GENE
 /* Bits of the device status word (sa_workspace_status). */
 enum sa_device_status {
     SA_DEV_OK = 0,
-    SA_DEV_PIPELINE_TIMEOUT = 1, /* a bounded wait on a copy barrier gave up        */
+    SA_DEV_PIPELINE_TIMEOUT = 1, /* a bounded wait (copy barrier, split states in
+                                    flight, a peer rank's state) gave up: the output
+                                    is incomplete and the workspace must be
+                                    zero-filled again before its next use          */
     SA_DEV_BAD_PAGE = 2          /* an active page_table entry was out of range and
                                     was skipped (never dereferenced)                */
 };
@@ -83,7 +86,9 @@ SA_API int sa_device_sm_count(int device);
  * ExactDecodePlan.build (backends/sm90/transposed_gqa_exact.py:332-347) and
  * make_paged_exact_workspace (kernels/paged_exact_triton.py:309-331).
  * The buffer must be zero-filled ONCE before its first use; calls leave it
- * ready for the next call.  Concurrent calls must not share a workspace.
+ * ready (all zero behind the status word) for the next call, unless a call
+ * reported SA_DEV_PIPELINE_TIMEOUT: then zero-fill it again.  Concurrent calls
+ * must not share a workspace.
  * num_ctas: 0 = automatic.  Depends only on its arguments (no device query). */
 SA_API size_t sa_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim, int num_ctas);
 
@@ -139,7 +144,12 @@ SA_API int sa_exact_decode(const void *q, const void *k, const void *v, void *ou
  *    outside any stream capture;
  *  - all calls on a device share the one array: calls that may overlap on the
  *    GPU (different streams) race and give wrong results.  Calls on one stream
- *    are safe; each call clears the counters it needs before launching.
+ *    are safe; each call clears the arrival counters it needs before launching
+ *    (one small cudaMemsetAsync on `stream` that the workspace entry points do
+ *    not pay);
+ *  - the device status bits of these calls collect in the array's status word;
+ *    read them with sa_static_status(), as sa_workspace_status() does for a
+ *    caller-provided workspace.
  */
 #define SA_STATIC_SCRATCH_BYTES (2 * 1024 * 1024)
 SA_API int sa_exact_decode_static(const void *q, const void *k, const void *v, void *out,
@@ -149,6 +159,12 @@ SA_API int sa_exact_decode_static(const void *q, const void *k, const void *v, v
                                   int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
                                   int dtype, int out_mode, int num_ctas, int kernel_choice,
                                   sa_stream_t stream);
+/* Status of the sa_exact_decode_static calls on the current device (no counterpart in the
+ * reference; allocates nothing): synchronise `stream`, return the sa_device_status bits collected
+ * since the last query and clear them.  A non-zero result also re-zeroes the built-in array, so
+ * the next call starts clean.  Negative on CUDA errors.  Without this query a wait that gave up
+ * would go unnoticed: the decode call itself returns before the kernel has run. */
+SA_API int sa_static_status(sa_stream_t stream);
 
 /*
  * Paged exact decode over a page pool with a page table and ragged per-row
@@ -232,7 +248,7 @@ SA_API int sa_merge_states(const float *states, int num_parts, int64_t rows, int
  * address of every rank's buffer as seen from this GPU (index = rank).  One call per decode step
  * on every rank, with the same step number (1, 2, 3, ...): the kernel stores local_state
  * [rows, D+2] into every rank's buffer with plain peer stores, raises this rank's flag there,
- * waits (at most 2 s, then SA_DEV_PIPELINE_TIMEOUT in the buffer's status word) for all ranks'
+ * waits (at most the wait limit, 2 s by default, then SA_DEV_PIPELINE_TIMEOUT in the buffer's status word) for all ranks'
  * flags and writes the merged out [rows, D].  Buffers are double-buffered by step parity.
  */
 #define SA_CP_MAX_WORLD 16
@@ -248,8 +264,9 @@ SA_API int sa_cp_exchange_status(void *exchange_buffer, int world_size, int64_t 
  * Context-parallel decode in ONE launch per step (no counterpart in the reference): the shard's
  * exact decode, the state exchange and the cross-rank merge fused.  The CTA that completes a
  * (row, KV head) pair on this rank stores the pair's state rows into every rank's exchange buffer
- * (plain peer stores), raises the pair's flag there, waits (at most 2 s, then
- * SA_DEV_PIPELINE_TIMEOUT in the workspace status word) for the same pair from all ranks and writes
+ * (plain peer stores; every 64-bit word carries the step number, so the data is its own flag),
+ * waits (at most the plan's wait limit, 2 s by default, then SA_DEV_PIPELINE_TIMEOUT in the
+ * workspace status word) for the same pair from all ranks and writes
  * the merged rows of out [batch, q_heads, D].  Up to 8 ranks; bf16/fp16, head_dim 64/128 (the
  * streaming kernel); uniform shard length.  Each rank's exchange buffer has
  * sa_cp_fused_bytes() bytes, is zero-filled once and addressable by all ranks; peer_buffers is a
@@ -304,6 +321,28 @@ SA_API int sa_plan_kernel(const sa_plan_t *plan);
 SA_API int sa_plan_num_ctas(const sa_plan_t *plan);
 SA_API int sa_plan_launches(const sa_plan_t *plan);
 SA_API void sa_plan_destroy(sa_plan_t *plan);
+
+/*
+ * Row subset of a bound plan: compute only the batch rows listed in the DEVICE array `rows`
+ * (index_dtype int32/int64, num_rows entries read at run time; entries outside [0, batch) are
+ * ignored, duplicates are harmless) and leave the output rows of every other batch row
+ * untouched.  rows = NULL restores "every row".  Replaces the row_indices argument of
+ * exact_decode_attention_rows_triton_forward_out_bhnd (kernels/gate0_exact_refresh_triton.py:
+ * 251-259, 266-344: "only selected rows are overwritten").  Not for fused context-parallel plans.
+ */
+SA_API int sa_plan_set_rows(sa_plan_t *plan, const void *rows, int index_dtype, int num_rows);
+
+/*
+ * Limit of the bounded device-side waits (TMA copy barriers, split states in flight between
+ * the CTAs of a launch, a peer rank's words in the context-parallel exchange).  A wait that
+ * runs out sets SA_DEV_PIPELINE_TIMEOUT in the status word and the kernel returns; nothing
+ * hangs or traps.  Default 2 s.  sa_set_wait_limit_ns sets the process-wide default that
+ * plans created afterwards, the one-shot calls and sa_cp_exchange_merge use;
+ * sa_plan_set_wait_limit_ns changes one plan.  No counterpart in the reference, whose
+ * kernels do not wait on each other.
+ */
+SA_API int sa_set_wait_limit_ns(uint64_t limit_ns);
+SA_API int sa_plan_set_wait_limit_ns(sa_plan_t *plan, uint64_t limit_ns);
 
 /* ---- KV-cache update: the step before each decode call ------------------------------------
  * Writes the current token's K/V row of every (row, KV head) into the cache at the row's

@@ -1,6 +1,7 @@
 // C-ABI entry points: argument validation, workspace layout, kernel selection,
 // TMA tensor-map construction and bound plans.  No torch types cross this file.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -17,6 +18,8 @@ namespace sa {
 namespace {
 
 thread_local char g_error[512] = "";
+thread_local bool g_workspace_too_small = false;  // why the last finish_plan() on this thread failed
+std::atomic<unsigned long long> g_default_wait_ns{kDefaultWaitNs};
 
 int fail(int code, const char *fmt, ...)
 {
@@ -249,12 +252,17 @@ int check_common(const void *q, const void *k, const void *v, const void *out, c
 int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t max_vlen, int kernel_choice)
 {
     Problem &p = plan->problem;
+    g_workspace_too_small = false;
+    p.wait_ns = g_default_wait_ns.load();
     p.sm_count = device_sm_count();
     if (p.sm_count <= 0 || cudaGetDevice(&plan->device) != cudaSuccess)
         return fail(SA_ERR_DEVICE, "no CUDA device is current");
     if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(SA_ERR_INVALID, "workspace must be 16-byte aligned");
     const size_t head = kStatusWords * 4 + counters_bytes(p.batch, p.q_heads);
-    if (workspace_bytes < head) return fail(SA_ERR_INVALID, "workspace too small");
+    if (workspace_bytes < head) {
+        g_workspace_too_small = true;
+        return fail(SA_ERR_INVALID, "workspace too small");
+    }
     p.ws.status = static_cast<int *>(workspace);
     p.ws.counters = p.ws.status + kStatusWords;
     p.ws.partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + head);
@@ -280,8 +288,10 @@ int finish_plan(sa_plan *plan, void *workspace, size_t workspace_bytes, int64_t 
                    ? generic_partial_floats(p.batch, p.q_heads, p.head_dim, plan->generic_splits)
                    : 0;
     }
-    if (need > p.ws.partial_floats)
+    if (need > p.ws.partial_floats) {
+        g_workspace_too_small = true;
         return fail(SA_ERR_INVALID, "workspace too small: need %zu bytes, got %zu", head + need * 4, workspace_bytes);
+    }
     return SA_OK;
 }
 
@@ -318,6 +328,7 @@ int fill_exact(sa_plan *plan, const void *q, const void *k, const void *v, void 
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
     p.q_sb = q_sb; p.q_sh = q_sh;
     p.seq.mode = kContig;
+    p.seq.num_rows = -1;
     p.seq.kv_sb = kv_sb; p.seq.kv_sn = kv_sn; p.seq.kv_sh = kv_sh;
     p.seq.kv_len = kv_len;
     p.seq.seq_lens = seq_lens;
@@ -348,6 +359,7 @@ int fill_paged(sa_plan *plan, const void *q, const void *k_pages, const void *v_
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
     p.q_sb = static_cast<int64_t>(q_heads) * head_dim; p.q_sh = head_dim;
     p.seq.mode = kPaged;
+    p.seq.num_rows = -1;
     p.seq.seq_lens = seq_lens;
     p.seq.lens_i64 = lens_dtype == SA_INDEX_I64;
     p.seq.page_table = page_table;
@@ -392,6 +404,7 @@ int fill_seed(sa_plan *plan, const void *q, const void *k, const void *v, void *
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
     p.q_sb = q_sb; p.q_sh = q_sh;
     p.seq.mode = kBlocks;
+    p.seq.num_rows = -1;
     p.seq.kv_sb = kv_sb; p.seq.kv_sn = kv_sn; p.seq.kv_sh = kv_sh;
     p.seq.kv_len = kv_len;
     p.seq.block_size = block_size;
@@ -645,17 +658,16 @@ int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_d
 namespace {
 
 struct FusedLayout {
-    size_t gather_floats_per_parity, flags_offset, total_bytes;
+    size_t gather_words_per_parity, total_bytes;
 };
 
 FusedLayout fused_layout(int world, int batch, int q_heads, int kv_heads, int head_dim)
 {
-    // gather[2][world][rows][D+2] of 8-byte {value, step} words; no separate flags.
+    // gather[2][world][rows][D+2] of 64-bit (step << 32 | value) words; the data is its own flag.
     (void)kv_heads;
     FusedLayout l;
-    l.gather_floats_per_parity = static_cast<size_t>(world) * batch * q_heads * (head_dim + 2);
-    l.flags_offset = (2 * l.gather_floats_per_parity * 8 + 127) / 128 * 128;
-    l.total_bytes = l.flags_offset + 128;
+    l.gather_words_per_parity = static_cast<size_t>(world) * batch * q_heads * (head_dim + 2);
+    l.total_bytes = (2 * l.gather_words_per_parity * 8 + 127) / 128 * 128 + 128;
     return l;
 }
 
@@ -705,12 +717,8 @@ sa_plan_t *sa_cp_fused_plan_create(const void *q, const void *k, const void *v, 
     plan->cp.rank = rank;
     plan->cp.step = 0;
     for (int i = 0; i < kCpMaxWorld; ++i) plan->cp.bases[i] = i < world_size ? peer_buffers[i] : 0;
-    plan->cp.gather_floats_per_parity = l.gather_floats_per_parity;
-    plan->cp.flags_offset = l.flags_offset;
+    plan->cp.gather_words_per_parity = l.gather_words_per_parity;
     plan->cp.final_out = out;
-#ifdef SA_TIMELINE
-    if (const char *e = std::getenv("SA_CP_DEBUG")) plan->cp.debug = std::atoi(e);
-#endif
     return plan;
 }
 
@@ -737,7 +745,7 @@ int sa_cp_exchange_merge(const float *local_state, const uint64_t *peer_buffers,
         if (peer_buffers[i] == 0 || peer_buffers[i] % 128)
             return fail(SA_ERR_INVALID, "sa_cp_exchange_merge: peer buffer %d is null or not 128-byte aligned", i);
     cudaError_t err = launch_exchange_merge(local_state, peer_buffers, world_size, rank, step, rows, head_dim, out,
-                                            out_dtype, static_cast<cudaStream_t>(stream));
+                                            out_dtype, g_default_wait_ns.load(), static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess) return fail_cuda(err, "sa_cp_exchange_merge");
     return SA_OK;
 }
@@ -799,17 +807,37 @@ int sa_exact_decode_static(const void *q, const void *k, const void *v, void *ou
     rc = fill_exact(&plan, q, k, v, out, scratch, SA_STATIC_SCRATCH_BYTES, seq_lens, lens_dtype, batch, q_heads,
                     kv_heads, head_dim, kv_len, q_stride_b, q_stride_h, kv_stride_b, kv_stride_n, kv_stride_h, dtype,
                     out_mode, num_ctas, kernel_choice);
-    if (rc == SA_ERR_INVALID && std::strstr(g_error, "workspace too small") != nullptr)
+    if (rc && g_workspace_too_small)
         return fail(SA_ERR_UNSUPPORTED,
                     "sa_exact_decode_static: this shape needs more than the %d bytes of built-in scratch; "
                     "use sa_exact_decode with a caller-provided workspace", SA_STATIC_SCRATCH_BYTES);
     if (rc) return rc;
-    // The array keeps whatever the previous call left.  The arrival counters and the
-    // status word must start at zero, so clear that prefix on the caller's stream.
-    const size_t prefix = kStatusWords * 4 + counters_bytes(batch, q_heads);
-    cudaError_t err = cudaMemsetAsync(scratch, 0, prefix, static_cast<cudaStream_t>(stream));
-    if (err != cudaSuccess) return fail_cuda(err, "sa_exact_decode_static: clearing the scratch prefix");
+    // The array keeps whatever the previous call left.  The arrival counters must start at
+    // zero, so clear them on the caller's stream (one small stream operation the workspace
+    // entry points do not need).  The status word in front of them is left alone: it collects
+    // the bits of every call until sa_static_status() reads and clears it.
+    cudaError_t err = cudaMemsetAsync(static_cast<char *>(scratch) + kStatusWords * 4, 0,
+                                      counters_bytes(batch, q_heads), static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_exact_decode_static: clearing the arrival counters");
     return run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int sa_static_status(sa_stream_t stream)
+{
+    void *scratch = nullptr;
+    if (static_scratch_address(&scratch)) return -SA_ERR_DEVICE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int word = 0;
+    cudaError_t err = cudaMemcpyAsync(&word, scratch, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    // A call that gave up a wait may have left split states behind: bring the whole array back
+    // to the all-zero state the kernels expect between calls.
+    if (err == cudaSuccess && word != 0) err = cudaMemsetAsync(scratch, 0, SA_STATIC_SCRATCH_BYTES, s);
+    if (err != cudaSuccess) {
+        fail_cuda(err, "sa_static_status");
+        return -SA_ERR_CUDA;
+    }
+    return word;
 }
 
 sa_plan_t *sa_exact_plan_create(const void *q, const void *k, const void *v, void *out, void *workspace,
@@ -892,6 +920,38 @@ int sa_plan_launches(const sa_plan_t *plan)
 }
 
 void sa_plan_destroy(sa_plan_t *plan) { delete plan; }
+
+int sa_set_wait_limit_ns(uint64_t limit_ns)
+{
+    if (limit_ns == 0) return fail(SA_ERR_INVALID, "sa_set_wait_limit_ns: the limit must be positive");
+    g_default_wait_ns.store(limit_ns);
+    return SA_OK;
+}
+
+int sa_plan_set_wait_limit_ns(sa_plan_t *plan, uint64_t limit_ns)
+{
+    if (!plan || limit_ns == 0) return fail(SA_ERR_INVALID, "sa_plan_set_wait_limit_ns: null plan or zero limit");
+    plan->problem.wait_ns = limit_ns;
+    return SA_OK;
+}
+
+int sa_plan_set_rows(sa_plan_t *plan, const void *rows, int index_dtype, int num_rows)
+{
+    if (!plan) return fail(SA_ERR_INVALID, "sa_plan_set_rows: null plan");
+    if (plan->cp.world > 0)
+        return fail(SA_ERR_UNSUPPORTED, "sa_plan_set_rows: a fused context-parallel plan computes every row");
+    if (rows == nullptr) {  // back to every row
+        plan->problem.seq.rows = nullptr;
+        plan->problem.seq.num_rows = -1;
+        return SA_OK;
+    }
+    if (num_rows < 0 || (index_dtype != SA_INDEX_I32 && index_dtype != SA_INDEX_I64))
+        return fail(SA_ERR_INVALID, "sa_plan_set_rows: num_rows must be >= 0 and the indices int32 or int64");
+    plan->problem.seq.rows = rows;
+    plan->problem.seq.rows_i64 = index_dtype == SA_INDEX_I64;
+    plan->problem.seq.num_rows = num_rows;
+    return SA_OK;
+}
 
 int sa_append_kv(const void *k_new, const void *v_new, void *k_cache, void *v_cache, const void *positions,
                  int pos_dtype, int num_positions, void *lens_out, const void *cos, const void *sin,

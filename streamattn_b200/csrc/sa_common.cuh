@@ -34,6 +34,11 @@ struct SeqDesc {
     // optional per-row lengths
     const void *seq_lens;
     int lens_i64;
+    // optional row subset: only the batch rows listed here are computed and written
+    // (entries outside [0, batch) are ignored, duplicates are harmless); num_rows < 0 = every row
+    const void *rows;
+    int rows_i64;
+    int num_rows;
     // paged addressing (elements): page*sp + slot*st + head*sh
     const void *page_table;
     int table_i64;
@@ -52,6 +57,16 @@ __host__ __device__ inline int64_t load_index(const void *p, int is_i64, int64_t
 {
     return is_i64 ? static_cast<const int64_t *>(p)[i]
                   : static_cast<int64_t>(static_cast<const int32_t *>(p)[i]);
+}
+
+// Whether batch row b is computed by this call (linear scan of the row list: for the kernels
+// that handle one row per CTA; the streaming kernel builds a table in shared memory instead).
+__device__ inline bool row_selected(const SeqDesc &s, int b)
+{
+    if (s.num_rows < 0) return true;
+    for (int i = 0; i < s.num_rows; ++i)
+        if (load_index(s.rows, s.rows_i64, i) == b) return true;
+    return false;
 }
 
 // Valid virtual length of row b.
@@ -86,7 +101,10 @@ struct Problem {
     int32_t *trace;
     int num_ctas;  // requested (0 = auto)
     int sm_count;
+    unsigned long long wait_ns;  // limit of every bounded device-side wait of the launch
 };
+
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // 2 s
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {
@@ -134,7 +152,7 @@ size_t exchange_bytes(int world, int64_t rows, int dim);
 size_t exchange_status_offset(int world, int64_t rows, int dim);
 cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *bases_host, int world, int rank,
                                   uint32_t step, int64_t rows, int dim, void *out, int out_dtype,
-                                  cudaStream_t stream);
+                                  unsigned long long wait_ns, cudaStream_t stream);
 
 struct StreamGeometry;  // defined in sa_stream.cuh
 

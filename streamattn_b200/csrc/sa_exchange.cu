@@ -20,7 +20,6 @@ namespace {
 constexpr int kExchangeMaxWorld = 16;
 constexpr int kExchangeThreads = 128;
 constexpr int kExchangeMaxCtas = 64;  // small enough to be co-resident: waiting CTAs cannot starve senders
-constexpr unsigned long long kExchangeWaitNs = 2000000000ull;
 
 struct ExchangeLayout {
     size_t gather_floats_per_parity;
@@ -50,6 +49,7 @@ struct ExchangeParams {
     int64_t rows;
     int dim;
     size_t gather_floats_per_parity, flags_offset, arrivals_offset, status_offset;
+    unsigned long long wait_ns;  // limit of the wait for the ranks' flags
     void *out;
 };
 
@@ -104,7 +104,7 @@ exchange_merge_kernel(const __grid_constant__ ExchangeParams p)
         while (true) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
             if (seen == p.step) break;
-            if (timer_ns() - t0 > kExchangeWaitNs) {
+            if (timer_ns() - t0 > p.wait_ns) {
                 atomicOr(reinterpret_cast<int *>(my_base + p.status_offset), SA_DEV_PIPELINE_TIMEOUT);
                 break;
             }
@@ -162,7 +162,7 @@ size_t exchange_status_offset(int world, int64_t rows, int dim) { return exchang
 
 cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *bases_host, int world, int rank,
                                   uint32_t step, int64_t rows, int dim, void *out, int out_dtype,
-                                  cudaStream_t stream)
+                                  unsigned long long wait_ns, cudaStream_t stream)
 {
     const ExchangeLayout l = exchange_layout(world, rows, dim);
     ExchangeParams p;
@@ -177,6 +177,7 @@ cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *base
     p.flags_offset = l.flags_offset;
     p.arrivals_offset = l.arrivals_offset;
     p.status_offset = l.status_offset;
+    p.wait_ns = wait_ns;
     p.out = out;
     const unsigned grid = static_cast<unsigned>(rows < kExchangeMaxCtas ? rows : kExchangeMaxCtas);
     switch (out_dtype) {

@@ -64,6 +64,7 @@ generic_partial_kernel(const __grid_constant__ GenericParams p)
     const int dim = p.head_dim;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    if (!row_selected(p.seq, b)) return;  // row subset: this row is neither computed nor written
     const T *q = static_cast<const T *>(p.q) + b * p.q_sb + h * p.q_sh;
     const T *kbase = static_cast<const T *>(p.k);
     const T *vbase = static_cast<const T *>(p.v);
@@ -170,14 +171,14 @@ generic_partial_kernel(const __grid_constant__ GenericParams p)
     }
 }
 
-// Exact merge of `parts` states per row:  m = max m_i, l = sum l_i 2^(m_i-m),
+// Exact merge of the `parts` states of one row:  m = max m_i, l = sum l_i 2^(m_i-m),
 // o = sum o_i 2^(m_i-m).  State i of row r starts at states + i*part_stride + r*row_stride.
+// `scrub` (or null) is the same memory as a writable pointer: the workspace's split states are
+// left zero-filled for the next launch, so they are cleared here after use.
 template <typename OutT>
-__global__ void __launch_bounds__(128)
-merge_states_kernel(const float *__restrict__ states, int parts, int64_t part_stride,
-                    int64_t row_stride, int dim, void *out, int out_mode)
+__device__ void merge_row(const float *states, int parts, int64_t part_stride, int64_t row_stride, int dim,
+                          void *out, int out_mode, float *scrub, int64_t row)
 {
-    const int64_t row = blockIdx.x;
     const float *base = states + row * row_stride;
     float big = -INFINITY;
     for (int i = 0; i < parts; ++i) {
@@ -204,6 +205,31 @@ merge_states_kernel(const float *__restrict__ states, int parts, int64_t part_st
         static_cast<float *>(out)[row * (dim + 2) + dim] = big;
         static_cast<float *>(out)[row * (dim + 2) + dim + 1] = total_l;
     }
+    if (scrub != nullptr) {
+        __syncthreads();  // every thread of the row has read what it needs
+        float *mine = scrub + row * row_stride;
+        for (int i = 0; i < parts; ++i)
+            for (int d = threadIdx.x; d < dim + 2; d += blockDim.x) mine[i * part_stride + d] = 0.0f;
+    }
+}
+
+// Merge of caller-provided states (sa_merge_states): one CTA per row.
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+merge_states_kernel(const float *__restrict__ states, int parts, int64_t part_stride, int64_t row_stride, int dim,
+                    void *out, int out_mode)
+{
+    merge_row<OutT>(states, parts, part_stride, row_stride, dim, out, out_mode, nullptr, blockIdx.x);
+}
+
+// Merge of the generic kernel's own split states (cleared after use; honours the row subset).
+template <typename T>
+__global__ void __launch_bounds__(128)
+merge_states_rows_kernel(const __grid_constant__ GenericParams p, int parts, int64_t part_stride, int64_t row_stride)
+{
+    const int64_t row = blockIdx.x;
+    if (!row_selected(p.seq, static_cast<int>(row / p.q_heads))) return;
+    merge_row<T>(p.partials, parts, part_stride, row_stride, p.head_dim, p.out, p.out_mode, p.partials, row);
 }
 
 template <typename T>
@@ -233,8 +259,9 @@ cudaError_t launch_generic_typed(const Problem &p, int splits, cudaStream_t stre
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess || splits == 1) return err;
     const int64_t stride = p.head_dim + 2;
-    merge_states_kernel<T><<<pairs, 128, 0, stream>>>(p.ws.partials, splits, stride, stride * splits,
-                                                      p.head_dim, p.out, p.out_mode);
+    // The row subset travels by value in the kernel's parameter block (a pointer to host memory
+    // would not do): reuse the descriptor inside the launch parameters of the first kernel.
+    merge_states_rows_kernel<T><<<pairs, 128, 0, stream>>>(gp, splits, stride, stride * splits);
     return cudaGetLastError();
 }
 

@@ -1,15 +1,16 @@
 // Streaming decode kernel for sm_100a: K/V tiles move HBM -> shared memory with
 // TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion,
-// no cluster multicast); every warp owns a private multi-stage ring of 16 KB
-// K+V tiles so the main loop has no cross-warp synchronisation.  QK^T and PV run
-// on the tensor cores (m16n8k16, query heads of one KV group on the M rows, fp32
-// accumulation) with a single-pass online softmax in the base-2 domain.
+// no cluster multicast); every warp owns a private ring of 16 KB K+V tiles so the
+// main loop has no cross-warp synchronisation.  QK^T and PV run on the tensor
+// cores (m16n8k16, query heads of one KV group on the M rows, fp32 accumulation)
+// with a single-pass online softmax in the base-2 domain.
 //
 // Work is a flat list of tiles over all (row, kv head) pairs, split over the CTAs in
 // contiguous slices (balanced by tokens, so ragged rows cost what they hold); a pair
-// is usually covered by several CTAs.  Each covering CTA writes an (m, l, o)
-// state; the last one to arrive (atomic ticket, no waiting) merges them exactly
-// and writes the output, so one launch does producer and merge.
+// is usually covered by several CTAs.  Each covering CTA publishes an (m, l, o)
+// state; the last one to arrive on the pair (a relaxed atomic ticket, nobody waits
+// for another CTA's progress) merges the states exactly and writes the output, so
+// one launch does producer and merge.
 //
 // The same kernel serves contiguous caches, paged caches (page-table lookup per
 // fragment) and seed-only decode (a short list of cache blocks).
@@ -31,7 +32,6 @@ namespace {
 #endif
 constexpr int kTileBytes = SA_STREAM_TILE_BYTES;  // one K or one V tile
 constexpr int kStageBytes = 2 * kTileBytes;  // K + V
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct StreamParams {
     const void *q;
@@ -55,32 +55,19 @@ struct StreamParams {
     int uniform_tiles;   // tiles per row when every row has the same length, else -1
     int schedule;        // kScheduleBlocked / kScheduleCyclic / kScheduleClaims
     int kv_split;        // virtual KV heads per physical KV head (kv_heads and group above are virtual)
+    unsigned long long wait_ns;  // limit of every bounded wait
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
-    unsigned long long *timeline;  // debug builds only: 8 globaltimer stamps per CTA
+    unsigned long long *timeline;  // instrumented builds only: 8 globaltimer stamps per CTA
 #endif
 };
 
+// Instrumented builds (-DSA_TIMELINE) record %globaltimer per CTA at a few points of the kernel.
 #ifdef SA_TIMELINE
-#define SA_STAMP_RAW(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
-#if SA_TIMELINE == 2
-#define SA_PSTAMP(i) SA_STAMP_RAW(i)
-#define SA_STAMP(i) do { if ((i) < 2) SA_STAMP_RAW(i); } while (0)
-#elif SA_TIMELINE == 3  // context-parallel tail: slots 1, 2, 7 = rows staged, rows sent, pair finished
-#define SA_CSTAMP(i) SA_STAMP_RAW(i)
-#define SA_STAMP(i) do { if ((i) != 1 && (i) != 7) SA_STAMP_RAW(i); } while (0)
-#else
-#define SA_STAMP(i) SA_STAMP_RAW(i)
-#endif
+#define SA_STAMP(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
 #else
 #define SA_STAMP(i) do { } while (0)
-#endif
-#ifndef SA_PSTAMP
-#define SA_PSTAMP(i) do { } while (0)
-#endif
-#ifndef SA_CSTAMP
-#define SA_CSTAMP(i) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -118,13 +105,13 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     return t;
 }
 
-// Bounded wait: gives up after kWaitLimitNs so a lost copy cannot hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+// Bounded wait: gives up after `limit_ns` so a lost copy cannot hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     while (!mbar_try_wait(bar, parity)) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
     return true;
 }
@@ -166,12 +153,61 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, u
                  : "r"(addr));
 }
 
-// Context-parallel exchange words: {value, step} written and read as one 8-byte access.
-__device__ __forceinline__ uint2 cp_load(const uint2 *src)
+// Split states travel between the CTAs of one launch as 32-bit words with all bits inverted.
+// The workspace is zero between launches, and no float the kernel can produce has the bit
+// pattern 0xffffffff (arithmetic results that are NaN carry the canonical pattern 0x7fffffff),
+// so a stored word is never zero: "word != 0" means "published", and a reader needs no flag,
+// fence or ordering beyond the single-copy atomicity of an aligned 32-bit access.  The merging
+// CTA writes zeros back after it has read a state.
+__device__ __forceinline__ uint4 state_load4(const float *src)
+{
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint2 state_load2(const float *src)
 {
     uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
+    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
     return v;
+}
+
+__device__ __forceinline__ void state_store4(float *dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void state_store2(float *dst, uint32_t a, uint32_t b)
+{
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(a), "r"(b) : "memory");
+}
+
+__device__ __forceinline__ uint32_t inv_bits(float x) { return ~__float_as_uint(x); }
+__device__ __forceinline__ float inv_float(uint32_t w) { return __uint_as_float(~w); }
+
+// Context-parallel exchange words: (step << 32 | float bits), written and read as one 64-bit
+// scalar (or a vector of two such scalars), which the memory model makes single-copy atomic:
+// a reader that sees the step number also has the value.
+__device__ __forceinline__ uint64_t cp_word(float value, uint32_t step)
+{
+    return (static_cast<uint64_t>(step) << 32) | __float_as_uint(value);
+}
+
+__device__ __forceinline__ ulonglong2 cp_load2(const uint64_t *src)
+{
+    ulonglong2 v;
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(src) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void cp_store2(uint64_t *dst, ulonglong2 v)
+{
+    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(v.x), "l"(v.y) : "memory");
 }
 
 template <typename T> struct Mma;
@@ -208,49 +244,40 @@ template <> struct Mma<__half> {
 
 // Send the tagged words of one pair's state rows - staged in shared memory by the finishing
 // CTA - to word offset `start` of every rank's buffer (own rank included).  Consecutive lanes
-// move consecutive 16-byte pieces, so one warp store covers 512 contiguous bytes: small scattered
-// stores are what NVLink handles worst.  Each 8-byte half carries its own step tag, so the copy
-// needs no ordering or atomicity beyond that of an aligned 8-byte access.
+// move consecutive 16-byte pieces (two words), so one warp store covers 512 contiguous bytes:
+// small scattered stores are what NVLink handles worst.  Every word carries its own step tag,
+// so the copy needs no ordering beyond the atomicity of an aligned 64-bit access.
 template <int NTHREADS>
-__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, const uint2 *stage, size_t start, size_t rank_stride,
-                                               int words, int tid)
+__device__ __noinline__ void cp_broadcast_pair(const CpFuse &cp, const uint64_t *stage, size_t start, int words,
+                                               int tid)
 {
-    const uint4 *src = reinterpret_cast<const uint4 *>(stage);
+    const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(stage);
     for (int i = tid; i < words / 2; i += NTHREADS) {  // `start` and `words` are even: 16-byte pieces
-        const uint4 v = src[i];
+        const ulonglong2 v = src[i];
         for (int k = 0; k < cp.world; ++k) {
             // Every rank starts with its right-hand neighbour, so the ranks - which finish a step
             // at about the same time - do not all write to the same destination at once.
             const int r = cp.rank + 1 + k < cp.world ? cp.rank + 1 + k : cp.rank + 1 + k - cp.world;
-#ifdef SA_CP_LOOPBACK  // debug builds: one GPU plays every rank (its rows land in all rank slots)
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[cp.rank]) + start +
-                                                   (static_cast<ptrdiff_t>(r) - cp.rank) * static_cast<ptrdiff_t>(rank_stride)) + i;
-#else
-            (void)rank_stride;
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint2 *>(cp.bases[r]) + start) + i;
-#endif
-            asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y),
-                         "r"(v.z), "r"(v.w)
-                         : "memory");
+            cp_store2(reinterpret_cast<uint64_t *>(cp.bases[r]) + start + 2 * i, v);
         }
     }
 }
 
 // Context-parallel finish of one (row, kv head) pair, run by the CTA that completed the pair on
 // this rank after it sent the pair's state rows to every rank: wait (bounded) for the same rows
-// from all ranks - each 8-byte word carries the step number, so the data is its own flag - then
-// merge them exactly and write the final output rows.  A work item is 4 columns of one head row;
+// from all ranks - each word carries the step number, so the data is its own flag - then merge
+// them exactly and write the final output rows.  A work item is 4 columns of one head row;
 // NTHREADS / items threads share an item and each polls every (NTHREADS / items)-th rank, four
 // ranks' (o[4], m, l) words at a time, so the wait costs one round of loads after the data
 // landed; the threads of an item meet through shared memory (`sm`, 6 floats per thread).  Kept
 // out of line so its registers do not weigh on the streaming loop.
 template <typename T, int D, int NTHREADS>
-__device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_t total_rows, int64_t out_row0,
-                                            int items, float *sm, int tid)
+__device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsigned long long wait_ns,
+                                            size_t total_rows, int64_t out_row0, int items, float *sm, int tid)
 {
     constexpr int STATE_STRIDE = D + 2;
     constexpr int RB = 4;  // ranks polled together by one thread
-    const uint2 *gather = reinterpret_cast<const uint2 *>(cp.bases[cp.rank]) + (cp.step & 1u) * cp.gather_floats_per_parity;
+    const uint64_t *gather = reinterpret_cast<const uint64_t *>(cp.bases[cp.rank]) + (cp.step & 1u) * cp.gather_words_per_parity;
     const size_t rank_stride = total_rows * STATE_STRIDE;
     const int parts = items <= NTHREADS ? NTHREADS / items : 1;
     const unsigned long long t0 = global_timer_ns();
@@ -263,51 +290,54 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_
         float big = -INFINITY, total_l = 0.0f;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (active) {
-            const uint2 *row0 = gather + (out_row0 + row) * STATE_STRIDE;
+            const uint64_t *row0 = gather + (out_row0 + row) * STATE_STRIDE;
             for (int r0 = part; r0 < cp.world; r0 += parts * RB) {
-                uint2 w[RB][6];
+                ulonglong2 w[RB][3];  // (o0, o1), (o2, o3), (m, l)
                 bool waiting = true;
                 while (waiting) {
-                    waiting = false;
+                    // Unconditional loads (ranks past the last one are clamped to it and given weight
+                    // zero below): one straight line of independent requests.
 #pragma unroll
                     for (int u = 0; u < RB; ++u) {
-                        const int r = r0 + u * parts;
-                        if (r < cp.world) {
-                            const uint2 *st = row0 + r * rank_stride;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) w[u][j] = cp_load(st + d4 + j);
-                            w[u][4] = cp_load(st + D);
-                            w[u][5] = cp_load(st + D + 1);
-#pragma unroll
-                            for (int j = 0; j < 6; ++j) waiting |= w[u][j].y != cp.step;
-                        }
+                        const int r = r0 + u * parts < cp.world ? r0 + u * parts : cp.world - 1;
+                        const uint64_t *st = row0 + r * rank_stride;
+                        w[u][0] = cp_load2(st + d4);
+                        w[u][1] = cp_load2(st + d4 + 2);
+                        w[u][2] = cp_load2(st + D);
                     }
-                    if (waiting && global_timer_ns() - t0 > kWaitLimitNs) {
+                    uint32_t landed = 1u;
+#pragma unroll
+                    for (int u = 0; u < RB; ++u)
+#pragma unroll
+                        for (int j = 0; j < 3; ++j)
+                            landed &= static_cast<uint32_t>(static_cast<uint32_t>(w[u][j].x >> 32) == cp.step) &
+                                      static_cast<uint32_t>(static_cast<uint32_t>(w[u][j].y >> 32) == cp.step);
+                    waiting = landed == 0u;
+                    if (waiting && global_timer_ns() - t0 > wait_ns) {
                         atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
                         break;
                     }
-#if defined(SA_TIMELINE) && SA_TIMELINE == 3
-                    if (waiting && (cp.debug & 2)) __nanosleep(300);  // experiment: poll less often
-#endif
                 }
+                auto val = [](uint64_t word) { return __uint_as_float(static_cast<uint32_t>(word)); };
+                float mr[RB];
                 float nb = big;
 #pragma unroll
-                for (int u = 0; u < RB; ++u)
-                    if (r0 + u * parts < cp.world) nb = fmaxf(nb, __uint_as_float(w[u][4].x));
+                for (int u = 0; u < RB; ++u) {
+                    mr[u] = r0 + u * parts < cp.world ? val(w[u][2].x) : -INFINITY;
+                    nb = fmaxf(nb, mr[u]);
+                }
                 const float keep = exp2_diff(big, nb);
                 acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
                 total_l *= keep;
                 big = nb;
 #pragma unroll
                 for (int u = 0; u < RB; ++u) {
-                    if (r0 + u * parts < cp.world) {
-                        const float wgt = exp2_diff(__uint_as_float(w[u][4].x), big);
-                        acc.x += wgt * __uint_as_float(w[u][0].x);
-                        acc.y += wgt * __uint_as_float(w[u][1].x);
-                        acc.z += wgt * __uint_as_float(w[u][2].x);
-                        acc.w += wgt * __uint_as_float(w[u][3].x);
-                        total_l += wgt * __uint_as_float(w[u][5].x);
-                    }
+                    const float wgt = exp2_diff(mr[u], big);  // 0 for the clamped duplicates
+                    acc.x += wgt * val(w[u][0].x);
+                    acc.y += wgt * val(w[u][0].y);
+                    acc.z += wgt * val(w[u][1].x);
+                    acc.w += wgt * val(w[u][1].y);
+                    total_l += wgt * val(w[u][2].y);
                 }
             }
         }
@@ -343,56 +373,101 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, size_
     }
 }
 
-// Exact merge of the `nseg` split states of one (row, kv head) pair by all threads of the CTA
-// (items <= NTHREADS).  A work item is 4 columns of one head row; NTHREADS / items threads share
-// an item and each takes every (NTHREADS / items)-th state, requesting its o rows together with
-// their (m, l) in one batch, so the whole merge costs one round trip to L2.  The per-thread
-// results meet in shared memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l).
-// Out of line so that the rows in flight do not weigh on the streaming loop's registers.
+// Exact merge of the `nseg` split states of one (row, kv head) pair by all threads of the
+// last CTA to arrive on it (items <= NTHREADS).  A work item is 4 columns of one head row;
+// NTHREADS / items threads share an item and each takes every (NTHREADS / items)-th state,
+// requesting its o rows together with their (m, l) in one batch, so the whole merge costs one
+// round trip to L2.  The CTA's own state (index `self`) does not make that trip: it is taken
+// from shared memory (`own`: o[4], m, l per item) and enters the sum at its index position, so
+// the order of the additions - and with it every bit of the result - does not depend on which
+// CTA happens to arrive last.
+// The other states are published with inverted bits (see state_load4): a word that still reads
+// zero has not landed yet and the batch is requested again, for at most `wait_ns`.  Every other
+// CTA of the pair took its ticket earlier, i.e. has left its streaming loop and is combining and
+// storing its state: the wait is for a few hundred nanoseconds of work of CTAs that are already
+// running, never for a CTA that still has to be scheduled.  The per-thread results meet in shared
+// memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l) and all nseg states are zero
+// again.  Out of line so that the rows in flight do not weigh on the streaming loop's registers.
 template <int D, int NTHREADS>
-__device__ __noinline__ void merge_pair_states(const float *first_slot, int64_t slot_stride, int nseg, int items,
-                                               float *sm, int tid)
+__device__ __noinline__ void merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
+                                               const float *own, int items, float *sm, int tid,
+                                               unsigned long long wait_ns, int *status)
 {
     constexpr int PART_STRIDE = D + 4;
-    constexpr int BATCH = 10;  // states per thread and pass: 20 split states (19 CTAs per pair at 8 pairs) in one pass
+    constexpr int BATCH = 10;  // states per thread and pass: 20 split states in one pass at two threads per item
     const int parts = NTHREADS / items;
     const int part = tid / items;
     const int item = tid - part * items;
     const bool active = part < parts;
     const int row = item / (D / 4);
     const int d4 = (item - row * (D / 4)) * 4;
-    const float *src = first_slot + row * PART_STRIDE;
+    float *src = first_slot + row * PART_STRIDE;
+    const int other = self == 0 ? 1 : 0;  // some state that is not the CTA's own (nseg >= 2)
     float big = -INFINITY, total_l = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    unsigned long long t0 = 0;
+    unsigned polls = 0;
     for (int i0 = part; active && i0 < nseg; i0 += parts * BATCH) {  // one pass up to BATCH * parts states
-        float4 o[BATCH];
-        float2 ml[BATCH];
+        // Every load of the batch is issued before the first result is looked at: the loads are
+        // unconditional (indices past the last state and the CTA's own index are redirected to
+        // another state and given weight zero below), so they form one straight line of
+        // independent requests - a branch per state would make each load wait for the one before.
+        uint4 o[BATCH];
+        uint2 ml[BATCH];
+        bool waiting = true;
+        while (waiting) {
 #pragma unroll
-        for (int u = 0; u < BATCH; ++u) {
-            const int i = i0 + u * parts;
-            if (i < nseg) {
-                o[u] = __ldcg(reinterpret_cast<const float4 *>(src + i * slot_stride + d4));
-                ml[u] = __ldcg(reinterpret_cast<const float2 *>(src + i * slot_stride + D));
-            } else {
-                o[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                ml[u] = make_float2(-INFINITY, 0.0f);
+            for (int u = 0; u < BATCH; ++u) {
+                int i = i0 + u * parts;
+                i = (i >= nseg || i == self) ? other : i;
+                o[u] = state_load4(src + i * slot_stride + d4);
+                ml[u] = state_load2(src + i * slot_stride + D);
+            }
+            uint32_t landed = 1u;
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u)
+                landed &= static_cast<uint32_t>(o[u].x != 0u) & static_cast<uint32_t>(o[u].y != 0u) &
+                          static_cast<uint32_t>(o[u].z != 0u) & static_cast<uint32_t>(o[u].w != 0u) &
+                          static_cast<uint32_t>(ml[u].x != 0u) & static_cast<uint32_t>(ml[u].y != 0u);
+            waiting = landed == 0u;
+            if (waiting && (++polls & 15) == 0) {  // the clock is slow to read: look at it now and then
+                const unsigned long long now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > wait_ns) {
+                    atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
+                    break;
+                }
             }
         }
+        {   // the CTA's own state takes its place in the sequence (stored like the others)
+            const float *mine = own + item * 6;
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                if (i0 + u * parts == self) {
+                    o[u] = make_uint4(inv_bits(mine[0]), inv_bits(mine[1]), inv_bits(mine[2]), inv_bits(mine[3]));
+                    ml[u] = make_uint2(inv_bits(mine[4]), inv_bits(mine[5]));
+                }
+            }
+        }
+        float mi[BATCH];
         float nb = big;
 #pragma unroll
-        for (int u = 0; u < BATCH; ++u) nb = fmaxf(nb, ml[u].x);
+        for (int u = 0; u < BATCH; ++u) {
+            mi[u] = i0 + u * parts < nseg ? inv_float(ml[u].x) : -INFINITY;
+            nb = fmaxf(nb, mi[u]);
+        }
         const float keep = exp2_diff(big, nb);
         acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
         total_l *= keep;
         big = nb;
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
-            const float wgt = exp2_diff(ml[u].x, big);
-            acc.x += wgt * o[u].x;
-            acc.y += wgt * o[u].y;
-            acc.z += wgt * o[u].z;
-            acc.w += wgt * o[u].w;
-            total_l += wgt * ml[u].y;
+            const float wgt = exp2_diff(mi[u], big);  // 0 for the redirected loads
+            acc.x += wgt * inv_float(o[u].x);
+            acc.y += wgt * inv_float(o[u].y);
+            acc.z += wgt * inv_float(o[u].z);
+            acc.w += wgt * inv_float(o[u].w);
+            total_l += wgt * inv_float(ml[u].y);
         }
     }
     if (active) {
@@ -401,18 +476,24 @@ __device__ __noinline__ void merge_pair_states(const float *first_slot, int64_t 
         *reinterpret_cast<float2 *>(mine + 2) = make_float2(acc.z, acc.w);
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
-    __syncthreads();
+    __syncthreads();  // every thread has read its states: they can be cleared
+    if (active) {
+        for (int i = part; i < nseg; i += parts) {
+            state_store4(src + i * slot_stride + d4, 0u, 0u, 0u, 0u);
+            if (d4 == 0) state_store2(src + i * slot_stride + D, 0u, 0u);
+        }
+    }
     if (part == 0 && parts > 1) {
         for (int q = 1; q < parts; ++q) {
-            const float *other = sm + (q * items + item) * 6;
-            const float ob = other[4];
+            const float *other_part = sm + (q * items + item) * 6;
+            const float ob = other_part[4];
             const float nb = fmaxf(big, ob);
             const float keep = exp2_diff(big, nb), wgt = exp2_diff(ob, nb);
-            acc.x = acc.x * keep + wgt * other[0];
-            acc.y = acc.y * keep + wgt * other[1];
-            acc.z = acc.z * keep + wgt * other[2];
-            acc.w = acc.w * keep + wgt * other[3];
-            total_l = total_l * keep + wgt * other[5];
+            acc.x = acc.x * keep + wgt * other_part[0];
+            acc.y = acc.y * keep + wgt * other_part[1];
+            acc.z = acc.z * keep + wgt * other_part[2];
+            acc.w = acc.w * keep + wgt * other_part[3];
+            total_l = total_l * keep + wgt * other_part[5];
             big = nb;
         }
         float *mine = sm + item * 6;
@@ -451,14 +532,17 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     constexpr int STATE_FLOATS = ROWS * STATE_STRIDE;  // one warp's (o, m, l) rows
     constexpr int NTHREADS = WARPS * 32;
     constexpr int BAR_BYTES = (WARPS * STAGES * 8 + 15) / 16 * 16;
+    constexpr int MERGE_ROWS = NTHREADS / (D / 4);  // head rows one merge pass covers
+    constexpr int OWN = (ROWS * (D / 4) + NTHREADS - 1) / NTHREADS;  // work items per thread
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + WARPS * STAGES * kStageBytes);
     float *states = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + BAR_BYTES);
-    uint2 *cp_stage = reinterpret_cast<uint2 *>(states + WARPS * STATE_FLOATS);  // context-parallel: rows to send
-    int *prefix = reinterpret_cast<int *>(cp_stage + STATE_FLOATS);            // ragged rows: tiles before row b
-    int *vlens = prefix + p.batch + 1;                                      // ragged rows: length of row b
+    uint64_t *cp_stage = reinterpret_cast<uint64_t *>(states + WARPS * STATE_FLOATS);  // context-parallel: rows to send
+    float *scratch = reinterpret_cast<float *>(cp_stage + STATE_FLOATS);  // merges: 6 floats per thread
+    int *prefix = reinterpret_cast<int *>(scratch + NTHREADS * 6);         // ragged rows: tiles before row b
+    int *vlens = prefix + p.batch + 1;                                     // ragged rows: length of row b (-1: not selected)
     __shared__ int s_last;
 
     const int tid = threadIdx.x;
@@ -477,13 +561,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     uint8_t *warp_ring = ring + warp * STAGES * kStageBytes;
 
     SA_STAMP(0);
-#if defined(SA_TIMELINE) && SA_TIMELINE == 1
-    if (p.timeline != nullptr && tid == 0) {
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        p.timeline[blockIdx.x * 8 + 2] = smid;
-    }
-#endif
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_v)) : "memory");
@@ -501,15 +578,31 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (ragged) {
         // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
+        const bool subset = p.seq.num_rows >= 0;
+        if (subset) {
+            // Row subset: rows that are not listed keep length -1 (no tiles, output untouched).
+            for (int b = tid; b < p.batch; b += NTHREADS) vlens[b] = -1;
+            __syncthreads();
+            for (int i = tid; i < p.seq.num_rows; i += NTHREADS) {
+                const int64_t r = load_index(p.seq.rows, p.seq.rows_i64, i);
+                if (r >= 0 && r < p.batch) vlens[r] = static_cast<int>(row_vlen(p.seq, static_cast<int>(r)));
+            }
+            __syncthreads();
+        }
         if (warp == 0) {
             int running = 0;
             for (int base = 0; base < p.batch; base += 32) {
                 const int b = base + lane;
                 int x = 0;
                 if (b < p.batch) {
-                    const int64_t n = row_vlen(p.seq, b);  // < 2^31: the host bounds the capacity
-                    vlens[b] = static_cast<int>(n);
-                    x = static_cast<int>((n + TILE_N - 1) / TILE_N);
+                    int n;
+                    if (subset) {
+                        n = vlens[b];
+                    } else {
+                        n = static_cast<int>(row_vlen(p.seq, b));  // < 2^31: the host bounds the capacity
+                        vlens[b] = n;
+                    }
+                    x = n > 0 ? (n + TILE_N - 1) / TILE_N : 0;
                 }
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
@@ -526,7 +619,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
     }
     fence_proxy_async();
-    SA_PSTAMP(2);
 
     const uint64_t policy = make_evict_first_policy();
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
@@ -670,7 +762,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         lo = range_lo(c);
         hi = range_lo(c + 1);
     }
-    SA_PSTAMP(3);
     // Static schedule: this warp's tiles are lo + warp + i*WARPS for i in [0, n_w), across all
     // segments of the CTA, so its copy pipeline keeps running through segment boundaries.
     // Dynamic schedule: tiles al_start + i*dyn_nw + dyn_gw for i <= STAGES, then one claim per tile.
@@ -795,7 +886,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     Frag first[STAGES + 1];
 #pragma unroll
     for (int s = 0; s <= STAGES; ++s) first[s] = lookup(next_tile());  // all table loads in flight together
-    SA_PSTAMP(4);
     int xq[STAGES];  // tiles in the ring, oldest first
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
@@ -806,8 +896,10 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     SA_STAMP(1);
 
     // Rows with no tokens are not part of the tile list: write their (empty) result here.
+    // Rows left out by a row subset (length -1) are not written at all.
     for (int b = c; b < p.batch; b += C) {
         if (tiles_before(b + 1) != tiles_before(b)) continue;
+        if (ragged && vlens[b] < 0) continue;
         for (int i = tid; i < p.q_heads * D; i += NTHREADS) {
             const int h = i / D, d = i % D;
             if (p.out_mode == SA_OUT_FINAL)
@@ -880,7 +972,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             const uint32_t parity = (static_cast<uint32_t>(j) / STAGES) & 1u;
             const uint32_t kb = ring_u32 + slot * kStageBytes;
             const uint32_t vb = kb + kTileBytes;
-            if (!dead && !mbar_wait(bar_u32 + slot * 8, parity)) {
+            if (!dead && !mbar_wait(bar_u32 + slot * 8, parity, p.wait_ns)) {
                 dead = true;
                 atomicOr(p.status, SA_DEV_PIPELINE_TIMEOUT);
             }
@@ -1066,26 +1158,25 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         const int64_t slot_stride = static_cast<int64_t>(group) * PART_STRIDE;
         float *my_slot = p.partials + (static_cast<int64_t>(c) + pair) * slot_stride;
         const int64_t out_row0 = static_cast<int64_t>(b) * p.q_heads + static_cast<int64_t>(kvh) * group;
+        const bool cp_on = p.cp.world > 0;
         auto store_result = [&](int row, int d4, const float4 &acc, float big, float total_l) {
             if (p.out_mode == SA_OUT_FINAL) {
                 const float inv = total_l > 0.0f ? 1.0f / total_l : 0.0f;
                 T *dst = static_cast<T *>(p.out) + (out_row0 + row) * D + d4;
                 *reinterpret_cast<uint2 *>(dst) =
                     make_uint2(Mma<T>::pack(acc.x * inv, acc.y * inv), Mma<T>::pack(acc.z * inv, acc.w * inv));
-            } else if (p.cp.world > 0) {
-                // Context-parallel: the pair's state rows are staged in shared memory as 8-byte
-                // words {value, step}; cp_broadcast_pair() then sends them to every rank's gather
-                // buffer with wide, lane-contiguous stores.  A word is written atomically, so a
-                // reader that sees the step number also sees the value - no fence or separate
-                // flag round trip.
-                uint2 *dst = cp_stage + row * STATE_STRIDE;
-                dst[d4] = make_uint2(__float_as_uint(acc.x), p.cp.step);
-                dst[d4 + 1] = make_uint2(__float_as_uint(acc.y), p.cp.step);
-                dst[d4 + 2] = make_uint2(__float_as_uint(acc.z), p.cp.step);
-                dst[d4 + 3] = make_uint2(__float_as_uint(acc.w), p.cp.step);
+            } else if (cp_on) {
+                // Context-parallel: the pair's state rows are staged in shared memory as tagged
+                // words; cp_broadcast_pair() then sends them to every rank's gather buffer with
+                // wide, lane-contiguous stores.
+                uint64_t *dst = cp_stage + row * STATE_STRIDE;
+                dst[d4] = cp_word(acc.x, p.cp.step);
+                dst[d4 + 1] = cp_word(acc.y, p.cp.step);
+                dst[d4 + 2] = cp_word(acc.z, p.cp.step);
+                dst[d4 + 3] = cp_word(acc.w, p.cp.step);
                 if (d4 == 0) {
-                    dst[D] = make_uint2(__float_as_uint(big), p.cp.step);
-                    dst[D + 1] = make_uint2(__float_as_uint(total_l), p.cp.step);
+                    dst[D] = cp_word(big, p.cp.step);
+                    dst[D + 1] = cp_word(total_l, p.cp.step);
                 }
             } else {
                 float *dst = static_cast<float *>(p.out) + (out_row0 + row) * STATE_STRIDE;
@@ -1095,7 +1186,26 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             }
         };
         const int items = group * (D / 4);
-        for (int item = tid; item < items; item += NTHREADS) {
+        // The pair's ticket is taken now, before this CTA's state is even combined: it counts the
+        // CTAs that have finished streaming and elects the last of them as the merger.  The
+        // merger recognises a state that has landed by its contents, so the ticket orders
+        // nothing, and its round trip overlaps the combine below.
+        int old_count = 0;
+        if (nseg > 1 && tid == 0)
+            asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], 1;"
+                         : "=r"(old_count)
+                         : "l"(p.counters + pair)
+                         : "memory");
+        // The thread keeps the items it combined (OWN of them at most) and parks them in shared
+        // memory once the warps' areas are free: if this CTA turns out to be the one that merges
+        // the pair, its own state never has to come back from global memory.
+        float own[OWN][6];
+#pragma unroll
+        for (int k = 0; k < OWN; ++k) {
+#pragma unroll
+            for (int e = 0; e < 6; ++e) own[k][e] = 0.0f;
+            const int item = tid + k * NTHREADS;
+            if (item >= items) continue;
             const int row = item / (D / 4);
             const int d4 = (item - row * (D / 4)) * 4;
             float big = -INFINITY;
@@ -1118,9 +1228,12 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             if (nseg == 1) {
                 store_result(row, d4, acc, big, total_l);
             } else {
+                // Publish with inverted bits: a word that reads non-zero has landed (state_load4).
                 float *dst = my_slot + row * PART_STRIDE;
-                *reinterpret_cast<float4 *>(dst + d4) = acc;
-                if (d4 == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(big, total_l);
+                state_store4(dst + d4, inv_bits(acc.x), inv_bits(acc.y), inv_bits(acc.z), inv_bits(acc.w));
+                if (d4 == 0) state_store2(dst + D, inv_bits(big), inv_bits(total_l));
+                own[k][0] = acc.x; own[k][1] = acc.y; own[k][2] = acc.z; own[k][3] = acc.w;
+                own[k][4] = big; own[k][5] = total_l;
             }
         }
 
@@ -1129,82 +1242,39 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             if (dyn_claims) p.pool[pair] = 0;  // every warp of the only CTA has made its last claim
         }
         if (nseg > 1) {
-            // Ticket with release/acquire semantics at GPU scope: together with the CTA barriers
-            // it orders every thread's state stores before the merging CTA's loads.
-            __syncthreads();
-            if (tid == 0) {
-                int old_count;
-                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
-                             : "=r"(old_count)
-                             : "l"(p.counters + pair)
-                             : "memory");
-                s_last = old_count == nseg - 1;
+            __syncthreads();  // the warps' state areas have been read by everybody
+#pragma unroll
+            for (int k = 0; k < OWN; ++k) {
+                const int item = tid + k * NTHREADS;
+                if (item < items) {
+                    float *dst = states + item * 6;
+                    *reinterpret_cast<float2 *>(dst) = make_float2(own[k][0], own[k][1]);
+                    *reinterpret_cast<float2 *>(dst + 2) = make_float2(own[k][2], own[k][3]);
+                    *reinterpret_cast<float2 *>(dst + 4) = make_float2(own[k][4], own[k][5]);
+                }
             }
+            if (tid == 0) s_last = old_count == nseg - 1;
             __syncthreads();
             SA_STAMP(5);
             if (s_last) {
-                // Last CTA to arrive on this pair: exact merge of its nseg split states.  All loads
-                // are issued before they are needed (the states sit in L2, ~1 us away).
-                const float *first_slot = p.partials + (static_cast<int64_t>(first_cta) + pair) * slot_stride;
-                if (items <= NTHREADS) {
-                    // The state areas are free again: the merged rows come back through them.
-                    merge_pair_states<D, NTHREADS>(first_slot, slot_stride, nseg, items, states, tid);
-                    if (tid < items) {
+                // Last CTA to arrive on this pair: exact merge of its nseg split states.
+                float *first_slot = p.partials + (static_cast<int64_t>(first_cta) + pair) * slot_stride;
+#pragma unroll
+                for (int k = 0; k < OWN; ++k) {
+                    const int r0 = k * MERGE_ROWS;
+                    if (r0 >= group) continue;
+                    const int n_rows = group - r0 < MERGE_ROWS ? group - r0 : MERGE_ROWS;
+                    const int sub_items = n_rows * (D / 4);
+                    merge_pair_states<D, NTHREADS>(first_slot + r0 * PART_STRIDE, slot_stride, nseg, c - first_cta,
+                                                   states + k * NTHREADS * 6, sub_items, scratch, tid, p.wait_ns,
+                                                   p.status);
+                    if (tid < sub_items) {
                         const int row = tid / (D / 4);
-                        const float *r = states + tid * 6;
-                        store_result(row, (tid - row * (D / 4)) * 4, make_float4(r[0], r[1], r[2], r[3]), r[4], r[5]);
+                        const float *r = scratch + tid * 6;
+                        store_result(r0 + row, (tid - row * (D / 4)) * 4, make_float4(r[0], r[1], r[2], r[3]), r[4],
+                                     r[5]);
                     }
-                } else {
-                constexpr int CAP = WARPS * STATE_FLOATS / 2;
-                float *sm_m = states;        // the state areas are free again: reuse them for (m, l)
-                float *sm_l = states + CAP;
-                const bool staged = group * nseg <= CAP;
-                if (staged) {
-                    for (int t = tid; t < group * nseg; t += NTHREADS) {
-                        const int i = t / group;
-                        const int row = t - i * group;
-                        const float2 ml = __ldcg(
-                            reinterpret_cast<const float2 *>(first_slot + i * slot_stride + row * PART_STRIDE + D));
-                        sm_m[row * nseg + i] = ml.x;
-                        sm_l[row * nseg + i] = ml.y;
-                    }
-                    __syncthreads();
-                }
-                for (int item = tid; item < items; item += NTHREADS) {
-                    const int row = item / (D / 4);
-                    const int d4 = (item - row * (D / 4)) * 4;
-                    const float *row_state = first_slot + row * PART_STRIDE;
-                    float big = -INFINITY;
-                    if (staged) {
-                        for (int i = 0; i < nseg; ++i) big = fmaxf(big, sm_m[row * nseg + i]);
-                    } else {
-#pragma unroll 4
-                        for (int i = 0; i < nseg; ++i) big = fmaxf(big, __ldcg(row_state + i * slot_stride + D));
-                    }
-                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    float total_l = 0.0f;
-#pragma unroll 8
-                    for (int i = 0; i < nseg; ++i) {
-                        const float *st = row_state + i * slot_stride;
-                        const float4 o = __ldcg(reinterpret_cast<const float4 *>(st + d4));
-                        float mi, li;
-                        if (staged) {
-                            mi = sm_m[row * nseg + i];
-                            li = sm_l[row * nseg + i];
-                        } else {
-                            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(st + D));
-                            mi = ml.x;
-                            li = ml.y;
-                        }
-                        const float wgt = exp2_diff(mi, big);
-                        acc.x += wgt * o.x;
-                        acc.y += wgt * o.y;
-                        acc.z += wgt * o.z;
-                        acc.w += wgt * o.w;
-                        total_l += wgt * li;
-                    }
-                    store_result(row, d4, acc, big, total_l);
-                }
+                    __syncthreads();  // the scratch is reused by the next rows
                 }
                 if (tid == 0) {  // ready for the next launch: every CTA of the pair has arrived
                     p.counters[pair] = 0;
@@ -1212,32 +1282,21 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 }
             }
         }
-        if (p.cp.world > 0 && (nseg == 1 || s_last)) {
-            __syncthreads();  // the pair's rows are complete in the staging area; the state areas are free
-            SA_CSTAMP(1);
+        if (cp_on && (nseg == 1 || s_last)) {
+            __syncthreads();  // the pair's rows are complete in the staging area
             cp_broadcast_pair<NTHREADS>(
                 p.cp, cp_stage,
-                (p.cp.step & 1u) * p.cp.gather_floats_per_parity +
+                (p.cp.step & 1u) * p.cp.gather_words_per_parity +
                     (static_cast<size_t>(p.cp.rank) * p.batch * p.q_heads + out_row0) * STATE_STRIDE,
-                static_cast<size_t>(p.batch) * p.q_heads * STATE_STRIDE, group * STATE_STRIDE, tid);
-#if defined(SA_TIMELINE) && SA_TIMELINE == 3
-            if (p.cp.debug & 1) __threadfence_system();  // experiment: push the peer stores out at once
-#endif
-            SA_CSTAMP(2);
-            cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, static_cast<size_t>(p.batch) * p.q_heads, out_row0, items,
-                                           states, tid);
-            SA_CSTAMP(7);
+                group * STATE_STRIDE, tid);
+            cp_finish_pair<T, D, NTHREADS>(p.cp, p.status, p.wait_ns, static_cast<size_t>(p.batch) * p.q_heads,
+                                           out_row0, items, scratch, tid);
         }
-        __syncthreads();  // the state areas and s_last are reused by the next segment
+        __syncthreads();  // the state areas, the scratch and s_last are reused by the next segment
         SA_STAMP(6);
         cur = seg_end;
     }
 }
-
-struct KernelEntry {
-    const void *fn;
-    size_t smem;
-};
 
 template <typename T, int D, int WARPS, int STAGES, bool ROWS16>
 cudaError_t launch_instance(const CUtensorMap &mk, const CUtensorMap &mv, const StreamParams &sp, int ctas,
@@ -1290,6 +1349,7 @@ cudaError_t launch_dim(const CUtensorMap &mk, const CUtensorMap &mv, const Strea
 }  // namespace
 
 #ifdef SA_TIMELINE
+// Instrumented builds only: where the kernels write their per-CTA time stamps (8 per CTA).
 unsigned long long *g_timeline = nullptr;
 extern "C" __attribute__((visibility("default"))) void sa_debug_timeline(void *ptr)
 {
@@ -1316,7 +1376,8 @@ size_t stream_smem_bytes(int head_dim, bool rows16, int stages, int batch)
     const size_t bars = (static_cast<size_t>(kStreamWarps) * stages * 8 + 15) / 16 * 16;
     // Per-warp (o, m, l) areas plus the context-parallel staging rows (8-byte words).
     const size_t states = (static_cast<size_t>(kStreamWarps) + 2) * (rows16 ? 16 : 8) * (head_dim + 2) * 4;
-    return 1024 + static_cast<size_t>(kStreamWarps) * stages * kStageBytes + bars + states +
+    const size_t scratch = static_cast<size_t>(kStreamWarps) * 32 * 6 * 4;  // merges: 6 floats per thread
+    return 1024 + static_cast<size_t>(kStreamWarps) * stages * kStageBytes + bars + states + scratch +
            (2 * static_cast<size_t>(batch) + 1) * 4 + 16;
 }
 
@@ -1347,8 +1408,10 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpF
     sp.fpt_shift = log2i(geo.frags_per_tile);
     sp.fpu_shift = log2i(geo.frags_per_unit);
     sp.tok_dim = geo.tok_dim;
-    sp.uniform_tiles = geo.uniform_tiles;
+    // A row subset makes the rows' tile counts differ (rows left out have none).
+    sp.uniform_tiles = p.seq.num_rows >= 0 ? -1 : geo.uniform_tiles;
     sp.schedule = geo.schedule;
+    sp.wait_ns = p.wait_ns;
     sp.seq = p.seq;
     sp.cp = cp;
 #ifdef SA_TIMELINE

@@ -26,18 +26,14 @@ enum StreamSchedule : int {
 };
 
 // Context-parallel exchange fused into the decode launch: where the ranks' gather buffers are.
-//   gather[2][world][rows][D+2] of 8-byte words {float bits, step}; gather_floats_per_parity counts words.
+//   gather[2][world][rows][D+2] of 64-bit words (step << 32 | float bits); gather_words_per_parity counts words.
 struct CpFuse {
     int world;  // 0 = not a context-parallel launch
     int rank;
     uint32_t step;
     uint64_t bases[kCpMaxWorld];
-    unsigned long long gather_floats_per_parity;
-    unsigned long long flags_offset;
+    unsigned long long gather_words_per_parity;
     void *final_out;  // [batch, q_heads, D] in the query dtype
-#ifdef SA_TIMELINE
-    int debug;        // debug builds only: experiment switches of the exchange
-#endif
 };
 
 struct StreamGeometry {

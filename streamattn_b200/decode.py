@@ -370,42 +370,43 @@ class Gate0SeedOnlyBatchedPolicy:
         layer_id: Optional[int] = None,
         backend_available: bool = True,
     ) -> List[str]:
-        """Fail-closed reasons, in the reference's order (decode.py:548-593)."""
+        """Why this policy refuses the call (empty list = it applies).
 
-        reasons: List[str] = []
-        if model_id is not None and model_id != self.model_id:
-            reasons.append("model_mismatch")
-        if layer_id is not None and int(layer_id) != self.layer_id:
-            reasons.append("layer_mismatch")
-        if not backend_available:
-            reasons.append("backend_unavailable")
-        if query.dim() != 4 or key.dim() != 4:
-            reasons.append("shape_mismatch")
-            return reasons
-        batch, query_len, heads, dim = (int(x) for x in query.shape)
-        key_batch, kv_len, kv_heads, key_dim = (int(x) for x in key.shape)
-        if (batch, dim) != (key_batch, key_dim):
-            reasons.append("shape_mismatch")
-        if query_len != 1:
-            reasons.append("query_len_mismatch")
-        if batch < self.min_batch:
-            reasons.append("batch_below_min")
-        if kv_len < min_kv_len:
-            reasons.append("kv_len_below_min")
-        if self.kv_len_bucket is not None and seq_bucket(kv_len) != seq_bucket(int(self.kv_len_bucket)):
-            reasons.append("kv_len_bucket_mismatch")
-        want = _normalize_dtype_name(self.dtype)
-        if want is not None and want != _normalize_dtype_name(query.dtype):
-            reasons.append("dtype_mismatch")
-        if kv_heads <= 0 or heads % kv_heads:
-            reasons.append("gqa_shape_mismatch")
-        if self.heads is not None and self.heads != heads:
-            reasons.append("heads_mismatch")
-        if self.kv_heads is not None and self.kv_heads != kv_heads:
-            reasons.append("kv_heads_mismatch")
-        if self.dim is not None and self.dim != dim:
-            reasons.append("head_dim_mismatch")
-        return reasons
+        The reason names and their order are the reference's (decode.py:548-593): callers log
+        and compare these lists.  Two tables: checks on the call's identity, then - only for
+        4-D tensors - checks on its shape; a check is a (name, refuses?) pair.
+        """
+
+        identity = (
+            ("model_mismatch", model_id is not None and model_id != self.model_id),
+            ("layer_mismatch", layer_id is not None and int(layer_id) != self.layer_id),
+            ("backend_unavailable", not backend_available),
+            ("shape_mismatch", query.dim() != 4 or key.dim() != 4),
+        )
+        reasons = [name for name, refuses in identity if refuses]
+        if reasons and reasons[-1] == "shape_mismatch":
+            return reasons  # nothing below can be read off tensors of another rank
+        batch, query_len, heads, dim = map(int, query.shape)
+        key_batch, kv_len, kv_heads, key_dim = map(int, key.shape)
+        dtype_wanted = _normalize_dtype_name(self.dtype)
+
+        def pinned_differs(pinned, actual) -> bool:
+            return pinned is not None and pinned != actual
+
+        shape = (
+            ("shape_mismatch", batch != key_batch or dim != key_dim),
+            ("query_len_mismatch", query_len != 1),
+            ("batch_below_min", batch < self.min_batch),
+            ("kv_len_below_min", kv_len < min_kv_len),
+            ("kv_len_bucket_mismatch",
+             self.kv_len_bucket is not None and seq_bucket(kv_len) != seq_bucket(int(self.kv_len_bucket))),
+            ("dtype_mismatch", pinned_differs(dtype_wanted, _normalize_dtype_name(query.dtype))),
+            ("gqa_shape_mismatch", kv_heads <= 0 or heads % kv_heads != 0),
+            ("heads_mismatch", pinned_differs(self.heads, heads)),
+            ("kv_heads_mismatch", pinned_differs(self.kv_heads, kv_heads)),
+            ("head_dim_mismatch", pinned_differs(self.dim, dim)),
+        )
+        return reasons + [name for name, refuses in shape if refuses]
 
     def matches_tensors(self, query: torch.Tensor, key: torch.Tensor, **kwargs) -> bool:
         return not self.mismatch_reasons(query, key, **kwargs)

@@ -1,16 +1,27 @@
-"""Public fixed-buffer decode engine (same surface as the reference's ``engine.py``).
+"""Fixed-buffer decode engine: resolve a route once, then launch without replanning.
 
-``StreamAttnEngine.plan(...)`` validates once, picks a route and binds it to the
-caller's Q/K/V buffers; ``StreamAttnEnginePlan.run()`` then launches without
-replanning.  Routes: ``exact_native``, ``seed_only_native`` and
-``verified_auto`` (policy-verified seed-only, fail-closed to exact with the
-reason recorded).  Reference: ``stream_attention/engine.py:37-323``.
+Public surface (names, arguments and defaults) follows the reference's
+``stream_attention/engine.py:37-323``: ``StreamAttnEngine.plan(q, k, v, mode=...)``
+returns a ``StreamAttnEnginePlan`` bound to the caller's buffers, ``.run()``
+launches it, ``StreamAttnEngine.decode`` / ``stream_attn_decode`` do both.
+
+Internally a call is handled in two steps.  ``_resolve_route`` turns (mode,
+cache kind, policy check) into a small ``_Route`` record - which kernel family
+serves the call and why - and ``_bind`` attaches the matching bound runner.
+Routes:
+
+========================  =====================================================
+``exact_native``          exact GQA decode (contiguous or paged cache)
+``seed_only_native``      seed-only decode; planning errors propagate
+``verified_auto``         seed-only when the packaged policy verifies the call,
+                          otherwise exact with the refusal reasons recorded
+========================  =====================================================
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Union
+from typing import Any, Callable, Dict, Optional, Union
 
 import torch
 
@@ -30,10 +41,26 @@ from .decode import (
 )
 from .paged import PagedExactDecodePlan, PagedExactDecodeRunner, PagedKVCache
 
+_Runner = Union[StreamAttnSeedOnlyDirectRunner, StreamAttnExactNativeDirectRunner, PagedExactDecodeRunner]
+
+_PAGED_REASON = {
+    STREAMATTN_MODE_EXACT_NATIVE: "explicit_paged_exact_native",
+    STREAMATTN_MODE_VERIFIED_AUTO: "paged_kv_exact_only",
+}
+
+
+@dataclass(frozen=True)
+class _Route:
+    """Outcome of route resolution: the kernel family, the recorded reason, the runner (if bound)."""
+
+    backend: str
+    reason: str
+    runner: Optional[_Runner]
+
 
 @dataclass(frozen=True)
 class StreamAttnEnginePlan:
-    """A decode plan bound to stable Q/K/V buffers."""
+    """Result of :meth:`StreamAttnEngine.plan`: a route plus the buffers it was bound to."""
 
     mode: str
     backend: str
@@ -44,31 +71,50 @@ class StreamAttnEnginePlan:
     key_cache: Union[torch.Tensor, PagedKVCache]
     value_cache: Optional[torch.Tensor]
     service: StreamAttnSeedOnlyDecodeService
-    direct_runner: Optional[
-        Union[StreamAttnSeedOnlyDirectRunner, StreamAttnExactNativeDirectRunner, PagedExactDecodeRunner]
-    ] = None
+    direct_runner: Optional[_Runner] = None
 
     @property
     def uses_fixed_buffers(self) -> bool:
+        """True when a bound runner exists, i.e. ``run()`` is a single attribute hop to a launch."""
+
         return self.direct_runner is not None
 
     def run(self, *, return_info: bool = True):
-        """Execute without replanning or policy parsing."""
+        """Launch on the bound buffers; returns ``(output, info)`` or just ``output``."""
 
-        runner = self.direct_runner
-        if runner is not None:
-            return runner.run_with_info() if return_info else runner.run()
-        if self.value_cache is None or not isinstance(self.key_cache, torch.Tensor):
+        if self.direct_runner is not None:
+            call = self.direct_runner.run_with_info if return_info else self.direct_runner.run
+            return call()
+        # Nothing could be bound (the kernels do not take these buffers).  The service then
+        # computes exact attention through the dense_fallback the caller injected, or raises:
+        # this package has no CPU execution path of its own.
+        if not isinstance(self.key_cache, torch.Tensor) or self.value_cache is None:
             raise RuntimeError("non-native plan is missing contiguous KV tensors")
-        # No bound runner (e.g. buffers the kernels cannot take): the service runs
-        # exact through the injected dense_fallback, or raises - there is no CPU path.
         return self.service.run(self.query, self.key_cache, self.value_cache, model_id=self.model_id,
                                 layer_id=self.layer_id, mode=STREAMATTN_MODE_EXACT_NATIVE,
                                 return_info=return_info)
 
 
+def _paged_serving_info(query: torch.Tensor, cache: PagedKVCache, plan: PagedExactDecodePlan,
+                        reason: str) -> StreamAttnServingInfo:
+    """Telemetry record of a paged exact plan (fields as the reference fills them, engine.py:119-160)."""
+
+    stats: Dict[str, Any] = {"layout": cache.normalized_layout, "page_size": cache.page_size}
+    stats["max_pages_per_request"] = cache.max_pages_per_request
+    stats["splits"] = plan.splits
+    stats["workspace_bytes"] = plan.workspace_bytes
+    counters = {"backend_counts": {plan.backend: 1}, "fallback_reasons": {}}
+    return StreamAttnServingInfo(
+        backend_used=plan.backend, plan_backend=plan.backend, plan_reason=reason,
+        policy_id=None, fallback_reason=None, model_id=None, layer_id=None,
+        batch_size=int(query.shape[0]), kv_len=int(cache.sequence_lengths.max().item()),
+        dtype=str(query.dtype).removeprefix("torch."), device=str(query.device),
+        seed_only_enabled=False, safety_policy_matched=False,
+        runtime_counters=counters, stats=stats)
+
+
 class StreamAttnEngine:
-    """Plan and run the native decode modes."""
+    """Plans and runs the native decode modes over caller-owned buffers."""
 
     def __init__(self, *, policy: Optional[Gate0SeedOnlyBatchedPolicy] = None,
                  policy_name: str = "qwen25_05b_l8_32k_seed_only_batched",
@@ -77,88 +123,77 @@ class StreamAttnEngine:
                  dense_fallback_backend: str = STREAMATTN_EXACT_NATIVE_BACKEND,
                  model_id: Optional[str] = None, layer_id: Optional[int] = None) -> None:
         self.service = StreamAttnSeedOnlyDecodeService(
-            policy=policy, policy_name=policy_name, decode_policy=decode_policy,
-            dense_fallback=dense_fallback, dense_fallback_backend=dense_fallback_backend,
-            model_id=model_id, layer_id=layer_id, use_planned_direct_seed_only_path=True,
-        )
+            policy=policy, policy_name=policy_name, decode_policy=decode_policy, dense_fallback=dense_fallback,
+            dense_fallback_backend=dense_fallback_backend, model_id=model_id, layer_id=layer_id,
+            use_planned_direct_seed_only_path=True)
 
-    def _exact_plan(self, *, mode, reason, model_id, layer_id, query, key_cache, value_cache) -> StreamAttnEnginePlan:
+    # -- route resolution ------------------------------------------------------------------
+
+    def _exact_route(self, reason: str, query, key_cache, value_cache, ids: Dict[str, Any]) -> _Route:
+        """Exact decode; when the buffers cannot be bound the route stays, without a runner."""
+
         try:
-            runner = self.service.plan_exact_native(query, key_cache, value_cache,
-                                                    model_id=model_id, layer_id=layer_id)
+            runner = self.service.plan_exact_native(query, key_cache, value_cache, **ids)
         except ValueError:
             runner = None
-        return StreamAttnEnginePlan(
-            mode=mode, backend=STREAMATTN_EXACT_NATIVE_BACKEND, reason=reason, model_id=model_id,
-            layer_id=layer_id, query=query, key_cache=key_cache, value_cache=value_cache,
-            service=self.service, direct_runner=runner,
-        )
+        return _Route(STREAMATTN_EXACT_NATIVE_BACKEND, reason, runner)
 
-    def _paged_exact_plan(self, *, mode: str, query: torch.Tensor, cache: PagedKVCache) -> StreamAttnEnginePlan:
-        if mode == STREAMATTN_MODE_SEED_ONLY_NATIVE:
+    def _paged_route(self, mode: str, query: torch.Tensor, cache: PagedKVCache) -> _Route:
+        if mode not in _PAGED_REASON:
             raise ValueError("seed_only_native does not yet support paged KV; use exact_native or verified_auto")
-        paged_plan = PagedExactDecodePlan.build(query, cache)
-        reason = "explicit_paged_exact_native" if mode == STREAMATTN_MODE_EXACT_NATIVE else "paged_kv_exact_only"
-        backend = paged_plan.backend
-        info = StreamAttnServingInfo(
-            backend_used=backend, policy_id=None, fallback_reason=None, batch_size=int(query.shape[0]),
-            kv_len=int(cache.sequence_lengths.max().item()), layer_id=None, model_id=None,
-            dtype=str(query.dtype).removeprefix("torch."), device=str(query.device), plan_backend=backend,
-            plan_reason=reason, seed_only_enabled=False, safety_policy_matched=False,
-            runtime_counters={"backend_counts": {backend: 1}, "fallback_reasons": {}},
-            stats={
-                "layout": cache.normalized_layout,
-                "page_size": cache.page_size,
-                "max_pages_per_request": cache.max_pages_per_request,
-                "splits": paged_plan.splits,
-                "workspace_bytes": paged_plan.workspace_bytes,
-            },
-        )
-        return StreamAttnEnginePlan(
-            mode=mode, backend=backend, reason=reason, model_id=None, layer_id=None, query=query,
-            key_cache=cache, value_cache=None, service=self.service,
-            direct_runner=PagedExactDecodeRunner(plan=paged_plan, info=info),
-        )
+        plan = PagedExactDecodePlan.build(query, cache)
+        reason = _PAGED_REASON[mode]
+        info = _paged_serving_info(query, cache, plan, reason)
+        return _Route(plan.backend, reason, PagedExactDecodeRunner(plan=plan, info=info))
+
+    def _resolve_route(self, mode: str, query, key_cache, value_cache, ids: Dict[str, Any]) -> _Route:
+        if mode == STREAMATTN_MODE_EXACT_NATIVE:
+            return self._exact_route("explicit_exact_native", query, key_cache, value_cache, ids)
+        try:
+            runner = self.service.plan_direct_seed_only(query, key_cache, value_cache, mode=mode, **ids)
+        except ValueError as refusal:
+            if mode == STREAMATTN_MODE_SEED_ONLY_NATIVE:
+                raise  # the caller asked for seed-only and nothing else
+            # verified_auto fails closed: exact decode, with the policy's refusal as the reason
+            return self._exact_route(str(refusal), query, key_cache, value_cache, ids)
+        return _Route(STREAMATTN_MODE_SEED_ONLY_NATIVE, "verified_policy_match", runner)
+
+    # -- public API ------------------------------------------------------------------------
 
     def plan(self, query: torch.Tensor, key_cache: Union[torch.Tensor, PagedKVCache],
              value_cache: Optional[torch.Tensor] = None, *, mode: str = STREAMATTN_MODE_VERIFIED_AUTO,
              model_id: Optional[str] = None, layer_id: Optional[int] = None) -> StreamAttnEnginePlan:
-        """Validate once and bind a native decode plan to stable buffers."""
+        """Check the call once, choose its route and bind it to the given buffers."""
 
         mode = normalize_stream_attn_mode(mode)
-        if isinstance(key_cache, PagedKVCache):
-            if value_cache is not None:
-                raise ValueError("value_cache must be omitted when key_cache is PagedKVCache")
-            return self._paged_exact_plan(mode=mode, query=query, cache=key_cache)
-        if value_cache is None:
+        paged = isinstance(key_cache, PagedKVCache)
+        if paged and value_cache is not None:
+            raise ValueError("value_cache must be omitted when key_cache is PagedKVCache")
+        if not paged and value_cache is None:
             raise ValueError("value_cache is required for contiguous KV decode")
-        model_id = model_id if model_id is not None else self.service.model_id
-        layer_id = layer_id if layer_id is not None else self.service.layer_id
-        bound = dict(model_id=model_id, layer_id=layer_id, query=query, key_cache=key_cache, value_cache=value_cache)
-        if mode == STREAMATTN_MODE_EXACT_NATIVE:
-            return self._exact_plan(mode=mode, reason="explicit_exact_native", **bound)
-        try:
-            runner = self.service.plan_direct_seed_only(query, key_cache, value_cache, model_id=model_id,
-                                                        layer_id=layer_id, mode=mode)
-        except ValueError as exc:
-            if mode == STREAMATTN_MODE_SEED_ONLY_NATIVE:
-                raise
-            return self._exact_plan(mode=mode, reason=str(exc), **bound)  # fail closed to exact
-        return StreamAttnEnginePlan(mode=mode, backend=STREAMATTN_MODE_SEED_ONLY_NATIVE,
-                                    reason="verified_policy_match", service=self.service,
-                                    direct_runner=runner, **bound)
+        if paged:
+            ids: Dict[str, Any] = {"model_id": None, "layer_id": None}
+            route = self._paged_route(mode, query, key_cache)
+        else:
+            ids = {"model_id": self.service.model_id if model_id is None else model_id,
+                   "layer_id": self.service.layer_id if layer_id is None else layer_id}
+            route = self._resolve_route(mode, query, key_cache, value_cache, ids)
+        return StreamAttnEnginePlan(mode=mode, backend=route.backend, reason=route.reason, query=query,
+                                    key_cache=key_cache, value_cache=value_cache, service=self.service,
+                                    direct_runner=route.runner, **ids)
 
     def decode(self, query, key_cache, value_cache=None, *, mode: str = STREAMATTN_MODE_VERIFIED_AUTO,
                model_id: Optional[str] = None, layer_id: Optional[int] = None, return_info: bool = True):
-        """Plan and execute one call; use :meth:`plan` for steady-state loops."""
+        """``plan(...)`` followed by one ``run()``; loops should keep the plan instead."""
 
-        return self.plan(query, key_cache, value_cache, mode=mode, model_id=model_id,
-                         layer_id=layer_id).run(return_info=return_info)
+        bound = self.plan(query, key_cache, value_cache, mode=mode, model_id=model_id, layer_id=layer_id)
+        return bound.run(return_info=return_info)
 
 
 def stream_attn_decode(query, key_cache, value_cache=None, *, mode: str = STREAMATTN_MODE_VERIFIED_AUTO,
                        engine: Optional[StreamAttnEngine] = None, return_info: bool = True, **engine_kwargs):
-    """One-shot decode entry point (``streamattn_b200.decode(...)``)."""
+    """One-shot decode (exported as ``decode``): uses ``engine`` or builds one from ``engine_kwargs``."""
 
-    runtime = engine or StreamAttnEngine(**engine_kwargs)
-    return runtime.decode(query, key_cache, value_cache, mode=mode, return_info=return_info)
+    if engine is None:
+        engine = StreamAttnEngine(**engine_kwargs)
+    return engine.decode(query, key_cache, value_cache, mode=mode, return_info=return_info)

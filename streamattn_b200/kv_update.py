@@ -305,29 +305,41 @@ class PagedKVWriter:
         return cls(cache=cache, pool=pool, lengths=lengths, pages=pages)
 
     def reserve(self, tokens: int = 1) -> int:
-        """Make sure every request has pages for ``tokens`` more tokens; returns pages assigned."""
+        """Make sure every request has pages for ``tokens`` more tokens; returns pages assigned.
+
+        All-or-nothing: every row's need is worked out and checked against the table capacity and
+        the pool first, and only then are pages taken and the device table written, so a refused
+        call leaves the pool, the host mirrors and the device table exactly as they were.
+        """
 
         page_size = self.cache.page_size
         max_pages = int(self.cache.page_table.shape[1])
-        rows: List[int] = []
-        slots: List[int] = []
-        ids: List[int] = []
+        wanted: List[Tuple[int, int, int]] = []  # (row, pages it has, pages it needs)
         for b, n in enumerate(self.lengths):
             need = -(-(n + tokens) // page_size)
             if need > max_pages:
                 raise ValueError("sequence lengths exceed page_table capacity")
-            have = len(self.pages[b])
-            if need > have:
-                fresh = self.pool.allocate(need - have)
-                rows.extend([b] * len(fresh))
-                slots.extend(range(have, need))
-                ids.extend(fresh)
-                self.pages[b].extend(fresh)
-        if ids:
-            table = self.cache.page_table
-            index = (torch.tensor(rows, device=table.device), torch.tensor(slots, device=table.device))
-            table.index_put_(index, torch.tensor(ids, dtype=table.dtype, device=table.device))
-        return len(ids)
+            if need > len(self.pages[b]):
+                wanted.append((b, len(self.pages[b]), need))
+        total = sum(need - have for _, have, need in wanted)
+        if total > self.pool.free_pages:
+            raise RuntimeError(f"out of KV pages: {total} requested, {self.pool.free_pages} free")
+        if total == 0:
+            return 0
+        fresh = self.pool.allocate(total)
+        rows: List[int] = []
+        slots: List[int] = []
+        taken = 0
+        for b, have, need in wanted:
+            mine = fresh[taken:taken + need - have]
+            taken += need - have
+            rows.extend([b] * len(mine))
+            slots.extend(range(have, need))
+            self.pages[b].extend(mine)
+        table = self.cache.page_table
+        index = (torch.tensor(rows, device=table.device), torch.tensor(slots, device=table.device))
+        table.index_put_(index, torch.tensor(fresh, dtype=table.dtype, device=table.device))
+        return total
 
     def append(self, key_new: torch.Tensor, value_new: torch.Tensor, **kwargs) -> Optional[torch.Tensor]:
         """Append one token to every request (assigning pages first); lengths advance on the device."""
@@ -338,12 +350,18 @@ class PagedKVWriter:
         return out
 
     def release(self, row: int) -> None:
-        """Give the pages of request ``row`` back to the pool (its table row becomes -1)."""
+        """Give the pages of request ``row`` back to the pool.
+
+        The row becomes an empty request on the host AND on the device: its table row is filled
+        with -1 and its entry of ``cache.sequence_lengths`` is set to 0 on the current stream, so
+        the next append writes position 0 of a fresh page and a decode in between reads nothing.
+        """
 
         self.pool.release(self.pages[row])
         self.pages[row] = []
         self.lengths[row] = 0
         self.cache.page_table[row].fill_(-1)
+        self.cache.sequence_lengths[row].fill_(0)
 
 
 __all__ = ["append_kv", "paged_append_kv", "AppendKVPlan", "PagePool", "PagedKVWriter"]

@@ -62,6 +62,7 @@ _SIGNATURES = {
     "sa_exact_decode": (_EXACT_ARGS + [_vp], _i),
     "sa_exact_decode_static": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i64,
                                 _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _vp], _i),
+    "sa_static_status": ([_vp], _i),
     "sa_paged_decode": (_PAGED_ARGS + [_vp], _i),
     "sa_seed_blocks": ([_i64, _i, _i, _i, _i, _i, _i32p, _i], _i),
     "sa_seed_token_indices": ([_i64, _i, _i32p, _i, _i64p, _i64], _i64),
@@ -82,6 +83,9 @@ _SIGNATURES = {
     "sa_plan_num_ctas": ([_vp], _i),
     "sa_plan_launches": ([_vp], _i),
     "sa_plan_destroy": ([_vp], None),
+    "sa_plan_set_rows": ([_vp, _vp, _i, _i], _i),
+    "sa_set_wait_limit_ns": ([ctypes.c_uint64], _i),
+    "sa_plan_set_wait_limit_ns": ([_vp, ctypes.c_uint64], _i),
     # k_new v_new k_cache v_cache | positions pos_dtype num_positions lens_out | cos sin rope_stride_b |
     # q_in q_out q_heads 4 q strides | batch kv_heads head_dim kv_len | 2 new strides | 3 kv strides | dtype status stream
     "sa_append_kv": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i64, _i64, _i64, _i64,
@@ -205,11 +209,35 @@ def new_workspace(device: torch.device, batch: int, q_heads: int, kv_heads: int,
 
 
 def workspace_status(workspace: torch.Tensor) -> int:
+    """Synchronise and return (then clear) the status bits of the kernels that used ``workspace``.
+
+    After ``SA_DEV_PIPELINE_TIMEOUT`` a launch may have left split states behind; the workspace
+    is zero-filled again here so that the next run starts from the state the kernels expect.
+    """
+
     with torch.cuda.device(workspace.device):
         rc = int(load().sa_workspace_status(workspace.data_ptr(), stream_handle(workspace.device)))
     if rc < 0:
         raise RuntimeError(last_error())
+    if rc & SA_DEV_PIPELINE_TIMEOUT:
+        workspace.zero_()
     return rc
+
+
+def static_status(device: torch.device) -> int:
+    """Status bits collected by :func:`exact_decode_static` calls on ``device`` (then cleared)."""
+
+    with torch.cuda.device(device):
+        rc = int(load().sa_static_status(stream_handle(device)))
+    if rc < 0:
+        raise RuntimeError(last_error())
+    return rc
+
+
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """Process-wide default limit of the kernels' bounded waits (plans created later, one-shot calls)."""
+
+    check(load().sa_set_wait_limit_ns(int(limit_ns)))
 
 
 def seed_blocks(kv_len: int, block_size: int, sink_blocks: int, recent_blocks: int,
@@ -260,6 +288,26 @@ class NativePlan:
         rc = self._run(self._handle, _current_raw_stream(self._device_index))
         if rc:
             check(rc)
+
+    def set_rows(self, rows: Optional[torch.Tensor]) -> None:
+        """Compute only the batch rows listed in the device tensor ``rows`` (``None``: every row)."""
+
+        if rows is None:
+            check(load().sa_plan_set_rows(self._handle, None, 0, 0))
+            self._rows = None
+            return
+        if rows.device != self._device or rows.dtype not in SA_INDEX or rows.dim() != 1 or not rows.is_contiguous():
+            raise ValueError("rows must be a contiguous 1-D int32/int64 tensor on the plan's device")
+        if rows.numel() == 0:  # an empty tensor has no storage: any valid device address will do
+            rows = torch.zeros(1, dtype=rows.dtype, device=rows.device)[:0]
+            pointer = rows.untyped_storage().data_ptr()
+        else:
+            pointer = rows.data_ptr()
+        check(load().sa_plan_set_rows(self._handle, pointer, SA_INDEX[rows.dtype], int(rows.numel())))
+        self._rows = rows  # keep the list alive: the kernel reads it at run time
+
+    def set_wait_limit_ns(self, limit_ns: int) -> None:
+        check(load().sa_plan_set_wait_limit_ns(self._handle, int(limit_ns)))
 
     def __del__(self) -> None:
         handle, self._handle = getattr(self, "_handle", None), None

@@ -168,6 +168,53 @@ def test_decode_loop_append_then_decode_matches_oracle(dev):
     assert writer.lengths == lengths == cache.sequence_lengths.cpu().tolist()
     assert plan.device_status() == 0
 
+@pytest.mark.gpu
+def test_released_row_is_reused_from_position_zero(dev):
+    """release(row) empties the request on the device too: the next appends start a fresh page at
+    position 0, a decode sees exactly the new tokens, and no bad-page status is raised."""
+
+    g = torch.Generator().manual_seed(7)
+    batch, q_heads, kv_heads, dim, page, max_pages = 2, 8, 2, 64, 16, 4
+    num_pages = 6
+    start = [20, 33]
+    kp = torch.zeros(num_pages, kv_heads, page, dim, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    table = torch.full((batch, max_pages), -1, dtype=torch.int32)
+    pool = PagePool(num_pages)
+    for b, n in enumerate(start):
+        ids = pool.allocate(-(-n // page))
+        table[b, : len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        for t in range(n):
+            kp[ids[t // page], :, t % page] = torch.randn(kv_heads, dim, generator=g).bfloat16()
+            vp[ids[t // page], :, t % page] = torch.randn(kv_heads, dim, generator=g).bfloat16()
+    cache = sa.PagedKVCache(key=kp.to(dev), value=vp.to(dev), page_table=table.to(dev),
+                            sequence_lengths=torch.tensor(start, dtype=torch.int32, device=dev), layout="HND")
+    writer = PagedKVWriter.attach(cache, pool)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    writer.release(1)
+    assert pool.free_pages == num_pages - 2 and cache.sequence_lengths.tolist() == [20, 0]
+    q = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16()
+    new_k, new_v = [], []
+    for _ in range(3):
+        k_new = torch.randn(batch, 1, kv_heads, dim, generator=g).bfloat16()
+        v_new = torch.randn(batch, 1, kv_heads, dim, generator=g).bfloat16()
+        writer.append(k_new.to(dev), v_new.to(dev), status=status)
+        new_k.append(k_new)
+        new_v.append(v_new)
+    assert int(status.item()) == 0
+    assert cache.sequence_lengths.tolist() == [23, 3] == writer.lengths
+    first_page = writer.pages[1][0]
+    for t in range(3):
+        assert torch.equal(cache.key[first_page, :, t].cpu(), new_k[t][1, 0])
+        assert torch.equal(cache.value[first_page, :, t].cpu(), new_v[t][1, 0])
+    plan = sa.PagedExactDecodePlan.build(q.to(dev), cache)
+    want = cpu_oracle.paged_decode(q, cache.key.cpu(), cache.value.cpu(), cache.page_table.cpu(),
+                                   cache.sequence_lengths.cpu(), layout="HND")
+    want = want[0] if isinstance(want, tuple) else want
+    diff = (plan.run().float().cpu() - want.float()).abs()
+    assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3
+    assert plan.device_status() == 0
+
 
 def test_bound_append_plan_and_decode_replay_in_a_cuda_graph(dev):
     """append + decode captured once and replayed: positions and lengths live on the device, so

@@ -75,3 +75,41 @@ def test_append_kv_has_no_cpu_path():
     new = torch.zeros(1, 2, 1, 64)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         append_kv(k, k.clone(), new, new.clone(), torch.zeros(1, dtype=torch.int64))
+
+
+def _cpu_writer(lengths, page=4, max_pages=3, num_pages=5):
+    from streamattn_b200 import PagedKVCache
+    from streamattn_b200.kv_update import PagedKVWriter, PagePool
+
+    pool = PagePool(num_pages)
+    table = torch.full((len(lengths), max_pages), -1, dtype=torch.int32)
+    for b, n in enumerate(lengths):
+        ids = pool.allocate(-(-n // page))
+        table[b, : len(ids)] = torch.tensor(ids, dtype=torch.int32)
+    cache = PagedKVCache(key=torch.zeros(num_pages, page, 1, 8), value=torch.zeros(num_pages, page, 1, 8),
+                         page_table=table, sequence_lengths=torch.tensor(lengths, dtype=torch.int32), layout="NHD")
+    return PagedKVWriter.attach(cache, pool), pool, cache
+
+
+def test_failed_reserve_leaves_pool_mirrors_and_table_untouched():
+    # rows hold 4 and 8 tokens = 1 + 2 pages of 5; the next token needs a page for each row, 2 are free
+    writer, pool, cache = _cpu_writer([4, 8], max_pages=4)
+    assert writer.reserve(1) == 2 and pool.free_pages == 0
+    writer.lengths = [8, 12]  # both rows full again: each needs another page, none is free
+    before = (pool.free_pages, [list(p) for p in writer.pages], cache.page_table.clone())
+    with pytest.raises(RuntimeError, match="out of KV pages"):
+        writer.reserve(1)
+    assert (pool.free_pages, writer.pages) == before[:2] and torch.equal(cache.page_table, before[2])
+    # capacity: row 1 would need a fourth table slot; row 0's need must not have been taken first
+    writer2, pool2, cache2 = _cpu_writer([4, 12], num_pages=8)
+    free = pool2.free_pages
+    with pytest.raises(ValueError, match="exceed page_table capacity"):
+        writer2.reserve(1)
+    assert pool2.free_pages == free and [len(p) for p in writer2.pages] == [1, 3]
+
+
+def test_release_resets_the_row_on_host_and_device_tensors():
+    writer, pool, cache = _cpu_writer([4, 8])
+    writer.release(1)
+    assert writer.lengths == [4, 0] and writer.pages[1] == [] and pool.free_pages == 4
+    assert cache.sequence_lengths.tolist() == [4, 0] and cache.page_table[1].tolist() == [-1, -1, -1]
