@@ -388,6 +388,21 @@ SA_API int sa_paged_append_kv(const void *k_new, const void *v_new, void *k_page
                               int64_t num_pages, int layout, int64_t new_stride_b, int64_t new_stride_h,
                               int dtype, int *status, sa_stream_t stream);
 
+/* ---- Output projection: the step after each decode call ----------------------------------
+ * out[b, n] = sum_k x[b, k] * weight[n, k] (+ bias[n]) for the few rows of a decode step, fp32
+ * accumulation, result in the input dtype (bf16/fp16).  Replaces qwen_o_proj_triton_forward
+ * (kernels/qwen_o_proj_triton.py:77-145; kernel :25-74), i.e. F.linear on [batch, 1, hidden].
+ *   x       [batch, in_features], rows x_stride_b elements apart (the attention output)
+ *   weight  [out_features, in_features] contiguous (PyTorch's layout);  bias [out_features] or NULL
+ *   out     [batch, out_features] contiguous
+ * in_features and x_stride_b must be multiples of 8, x and weight 16-byte aligned.
+ * prefetch_weights != 0: the kernel may start reading weight (never x) before earlier work of
+ * `stream` has finished, which hides the weight stream behind the tail of the attention kernel;
+ * pass 0 if the weights are written by work that was enqueued on `stream` just before. */
+SA_API int sa_o_proj(const void *x, const void *weight, const void *bias, void *out,
+                     int batch, int in_features, int out_features, int64_t x_stride_b,
+                     int dtype, int prefetch_weights, sa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -189,3 +189,17 @@ def paged_rope_append(q_raw, k_raw, v_raw, cos, sin, key_pages, value_pages, pag
             key_pages[page, :, slot] = k_rot[b, :, 0, :]
             value_pages[page, :, slot] = v_raw[b, :, 0, :]
     return q_rot
+
+
+def o_proj(attn_output: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Output projection of a decode step in float32 on the CPU: ``F.linear`` on ``[batch, 1, hidden]``.
+
+    The reference's kernel for this step is Triton-only (kernels/qwen_o_proj_triton.py:25-145) and
+    its own test checks it against ``F.linear`` (tests/test_qwen_o_proj_triton.py:19-30); this is
+    that checker, evaluated in float32 on the exact input values.
+    """
+
+    x = attn_output.detach().to("cpu", torch.float32)
+    w = weight.detach().to("cpu", torch.float32)
+    b = None if bias is None else bias.detach().to("cpu", torch.float32)
+    return torch.nn.functional.linear(x, w, b)

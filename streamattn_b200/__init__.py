@@ -47,13 +47,29 @@ from .exact import ExactDecodePlan, choose_num_splits
 from .paged import (
     PAGED_EXACT_NATIVE_BACKEND,
     PAGED_EXACT_SM100_BACKEND,
+    PAGED_EXACT_SM90_FRAGMENTED_RAGGED_BACKEND,
     PagedExactDecodePlan,
     PagedKVCache,
     choose_paged_exact_splits,
+    paged_exact_reference,
     stream_attn_paged_exact_decode,
 )
+from .seed_autotune import (
+    SeedKernelAutotuneResult,
+    SeedKernelCandidate,
+    SeedKernelShape,
+    autotune_seed_kernel_mode,
+    seed_kernel_candidates,
+    seed_shape_from_policy,
+)
+from .bucket_policy import (
+    BucketRouteDecision,
+    qwen25_3b_bucket_route_decision,
+    qwen25_3b_policy_names_for_bucket,
+)
+from .o_proj import OProjPlan, qwen_o_proj_forward
 from .kv_update import AppendKVPlan, PagedKVWriter, PagePool, append_kv, paged_append_kv
-from .seed_schedule import policy_seed_blocks, seed_indices, seed_token_indices_from_blocks
+from .seed_selectors import policy_seed_blocks, seed_indices, seed_token_indices_from_blocks
 
 # ``import streamattn_b200 as stream_attn; stream_attn.decode(...)``
 decode = stream_attn_decode

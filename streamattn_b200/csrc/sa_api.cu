@@ -953,6 +953,25 @@ int sa_plan_set_rows(sa_plan_t *plan, const void *rows, int index_dtype, int num
     return SA_OK;
 }
 
+int sa_o_proj(const void *x, const void *weight, const void *bias, void *out, int batch, int in_features,
+              int out_features, int64_t x_stride_b, int dtype, int prefetch_weights, sa_stream_t stream)
+{
+    if (!x || !weight || !out) return fail(SA_ERR_INVALID, "sa_o_proj: null tensor pointer");
+    if (batch <= 0 || in_features <= 0 || out_features <= 0)
+        return fail(SA_ERR_INVALID, "sa_o_proj: batch and feature counts must be positive");
+    if (dtype != SA_DTYPE_BF16 && dtype != SA_DTYPE_F16) return fail(SA_ERR_INVALID, "sa_o_proj: dtype must be bf16 or fp16");
+    if (x_stride_b < in_features) return fail(SA_ERR_INVALID, "sa_o_proj: x_stride_b smaller than in_features");
+    if (in_features % 8 || x_stride_b % 8 || reinterpret_cast<uintptr_t>(x) % 16 ||
+        reinterpret_cast<uintptr_t>(weight) % 16)
+        return fail(SA_ERR_UNSUPPORTED,
+                    "sa_o_proj: in_features and x_stride_b must be multiples of 8 and x / weight 16-byte aligned");
+    if (batch > 65535 * 16) return fail(SA_ERR_UNSUPPORTED, "sa_o_proj: batch too large");
+    const cudaError_t err = launch_o_proj(x, weight, bias, out, batch, in_features, out_features, x_stride_b, dtype,
+                                          prefetch_weights != 0, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_o_proj");
+    return SA_OK;
+}
+
 int sa_append_kv(const void *k_new, const void *v_new, void *k_cache, void *v_cache, const void *positions,
                  int pos_dtype, int num_positions, void *lens_out, const void *cos, const void *sin,
                  int64_t rope_stride_b, const void *q_in, void *q_out, int q_heads, int64_t q_in_stride_b,

@@ -154,6 +154,9 @@ cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *base
                                   uint32_t step, int64_t rows, int dim, void *out, int out_dtype,
                                   unsigned long long wait_ns, cudaStream_t stream);
 
+cudaError_t launch_o_proj(const void *x, const void *w, const void *bias, void *out, int batch, int in_features,
+                          int out_features, int64_t x_stride, int dtype, int prefetch_weights, cudaStream_t stream);
+
 struct StreamGeometry;  // defined in sa_stream.cuh
 
 }  // namespace sa

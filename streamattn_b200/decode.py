@@ -26,7 +26,7 @@ from typing import Any, Callable, Dict, List, Optional, Union
 import torch
 
 from . import native
-from .seed_schedule import policy_seed_blocks
+from .seed_selectors import policy_seed_blocks
 
 DenseFallbackFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor]
 
@@ -583,12 +583,22 @@ class StreamAttnSeedOnlyDirectRunner(_BoundRunner):
                  info: StreamAttnServingInfo, kernel: str = "auto") -> None:
         super().__init__(query, key_cache, value_cache, output, info)
         self.policy = policy
-        self.seed_blocks = policy.seed_blocks(int(key_cache.shape[1]))
+        kv_len, kv_heads = int(key_cache.shape[1]), int(key_cache.shape[2])
+        self.seed_blocks = policy.seed_blocks(kv_len)
         batch, _, q_heads, dim = (int(x) for x in query.shape)
-        self.workspace = native.new_workspace(query.device, batch, q_heads, int(key_cache.shape[2]), dim)
+        # Grid of the launch: CTAs per (row, KV head) pair from the latency model of the kernel
+        # (few seed tokens: one CTA per pair and no merge; many: the pair is split).
+        from .seed_autotune import SeedKernelShape, autotune_seed_kernel_mode
+
+        shape = SeedKernelShape(batch=batch, q_heads=q_heads, kv_heads=kv_heads, kv_len=kv_len, dim=dim,
+                                block_size=policy.block_size, sink_blocks=len(self.seed_blocks),
+                                recent_blocks=0, middle_seed_blocks=0, dtype_bytes=query.element_size())
+        self.grid = autotune_seed_kernel_mode(shape, sm_count=native.sm_count(query.device))
+        num_ctas = self.grid.recommended_num_ctas if query.is_cuda else 0
+        self.workspace = native.new_workspace(query.device, batch, q_heads, kv_heads, dim, num_ctas)
         self._plan = native.seed_plan(query, key_cache, value_cache, output, self.workspace,
                                       block_size=policy.block_size, blocks=self.seed_blocks,
-                                      kv_layout="BNHD", kernel=kernel)
+                                      kv_layout="BNHD", num_ctas=num_ctas, kernel=kernel)
         self.backend_variant = self._plan.kernel_name
 
     def run(self) -> torch.Tensor:

@@ -86,6 +86,7 @@ _SIGNATURES = {
     "sa_plan_set_rows": ([_vp, _vp, _i, _i], _i),
     "sa_set_wait_limit_ns": ([ctypes.c_uint64], _i),
     "sa_plan_set_wait_limit_ns": ([_vp, ctypes.c_uint64], _i),
+    "sa_o_proj": ([_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp], _i),
     # k_new v_new k_cache v_cache | positions pos_dtype num_positions lens_out | cos sin rope_stride_b |
     # q_in q_out q_heads 4 q strides | batch kv_heads head_dim kv_len | 2 new strides | 3 kv strides | dtype status stream
     "sa_append_kv": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i64, _i64, _i64, _i64,
@@ -180,6 +181,13 @@ def require_cuda(*tensors: torch.Tensor, host_io: Sequence[torch.Tensor] = ()) -
 def device_supported(device: torch.device) -> bool:
     index = device.index if device.index is not None else torch.cuda.current_device()
     return bool(load().sa_device_supported(int(index)))
+
+
+def sm_count(device: torch.device) -> int:
+    """Streaming multiprocessors of ``device`` (148 on a B200)."""
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return int(load().sa_device_sm_count(int(index))) or 148
 
 
 _current_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)

@@ -20,6 +20,11 @@ from . import native
 
 PAGED_EXACT_NATIVE_BACKEND = "streamattn_paged_exact_native"
 PAGED_EXACT_SM100_BACKEND = "streamattn_paged_sm100_exact"
+# Names of the reference's sm_90 backends.  One sm_100 kernel serves contiguous, fragmented and
+# ragged page tables alike, so all of them name the backend a plan on this package reports.
+PAGED_EXACT_SM90_BACKEND = PAGED_EXACT_SM100_BACKEND
+PAGED_EXACT_SM90_FRAGMENTED_BACKEND = PAGED_EXACT_SM100_BACKEND
+PAGED_EXACT_SM90_FRAGMENTED_RAGGED_BACKEND = PAGED_EXACT_SM100_BACKEND
 
 
 @dataclass(frozen=True)
@@ -233,3 +238,52 @@ def stream_attn_paged_exact_decode(query: torch.Tensor, cache: PagedKVCache, *,
     """Plan and execute one exact paged-KV decode call."""
 
     return PagedExactDecodePlan.build(query, cache, output=output, splits=splits).run()
+
+
+def paged_exact_reference(query: torch.Tensor, cache: PagedKVCache, *,
+                          output: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Page-by-page exact attention in plain tensor operations, for CHECKING results.
+
+    Same contract as the reference's ``paged_exact_reference`` (paged.py:201-256): walks each
+    request's page table in order, never gathers the pages into a contiguous cache, keeps a
+    running (max, denominator, numerator) per query head in float32.  It runs wherever the
+    tensors live and is slow by construction (a Python loop over pages).  Nothing in this
+    package calls it: decode always goes through the sm_100a kernels and raises on tensors
+    they cannot take.
+    """
+
+    cache.validate(query)
+    if output is None:
+        output = torch.empty_like(query)
+    if output.shape != query.shape or output.dtype != query.dtype:
+        raise ValueError("output must match query shape and dtype")
+    if output.device != query.device or not output.is_contiguous():
+        raise ValueError("output must be contiguous and share the query device")
+    batch, _, heads, dim = (int(x) for x in query.shape)
+    page, kv_heads = cache.page_size, cache.kv_heads
+    group = heads // kv_heads
+    hnd = cache.normalized_layout == "HND"
+    scale = float(dim) ** -0.5
+    lengths = [int(n) for n in cache.sequence_lengths.tolist()]
+    table = cache.page_table.tolist()
+    for b, n in enumerate(lengths):
+        q = query[b, 0].float().view(kv_heads, group, dim)                      # [Hkv, G, D]
+        top = torch.full((kv_heads, group), -float("inf"), dtype=torch.float32, device=query.device)
+        den = torch.zeros_like(top)
+        num = torch.zeros(kv_heads, group, dim, dtype=torch.float32, device=query.device)
+        for slot in range(-(-n // page)):
+            valid = min(page, n - slot * page)
+            k_page, v_page = cache.key[table[b][slot]], cache.value[table[b][slot]]
+            if hnd:                                                              # -> [Hkv, valid, D]
+                k_page, v_page = k_page[:, :valid], v_page[:, :valid]
+            else:
+                k_page, v_page = k_page[:valid].transpose(0, 1), v_page[:valid].transpose(0, 1)
+            scores = torch.einsum("hgd,htd->hgt", q, k_page.float()) * scale
+            new_top = torch.maximum(top, scores.amax(dim=-1))
+            keep = torch.exp(top - new_top)
+            weights = torch.exp(scores - new_top[..., None])
+            num = num * keep[..., None] + torch.einsum("hgt,htd->hgd", weights, v_page.float())
+            den = den * keep + weights.sum(dim=-1)
+            top = new_top
+        output[b, 0].copy_((num / den[..., None]).view(heads, dim).to(output.dtype))
+    return output

@@ -311,6 +311,42 @@ def host_contract_goldens(ref) -> None:
     (HERE / "host_contract.json").write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n")
 
 
+def route_policy_goldens(ref) -> None:
+    """Pure-Python routing helpers next to the decode path: the Qwen2.5-3B bucket route decisions
+    (bucket_policy.py:52-211) and the shape record of the seed-kernel autotuner
+    (seed_autotune.py:17-104, 333-354), as the reference computes them."""
+
+    import itertools
+
+    buckets = [None, "", "default", "needle", "code", "long_doc", "chat_doc", "mixed_validated",
+               "chat_instruction", "json_tool", "needle_rag", "noisy_neartie", "never_seen"]
+    tiers = [None, "bucket_only", "validated", "stress", "unknown"]
+    decisions = []
+    for bucket, strict, tier in itertools.product(buckets, [True, False], tiers):
+        d = ref.qwen25_3b_bucket_route_decision(bucket, product_strict=strict, risk_tier=tier)
+        decisions.append({"bucket": bucket, "product_strict": strict, "risk_tier": tier, "decision": asdict(d),
+                          "policy_names": list(ref.qwen25_3b_policy_names_for_bucket(
+                              bucket, product_strict=strict, risk_tier=tier))})
+    shapes = []
+    for batch, q_heads, kv_heads, kv_len, dim, bs, sink, recent, middle in [
+            (8, 16, 2, 32768, 128, 32, 2, 2, 8), (1, 16, 2, 32768, 128, 32, 2, 3, 0), (4, 14, 2, 32768, 64, 32, 2, 6, 12),
+            (2, 8, 8, 100, 64, 16, 4, 4, 4), (3, 32, 8, 65536, 128, 16, 4, 16, 4)]:
+        shape = ref.SeedKernelShape(batch=batch, q_heads=q_heads, kv_heads=kv_heads, kv_len=kv_len, dim=dim,
+                                    block_size=bs, sink_blocks=sink, recent_blocks=recent, middle_seed_blocks=middle)
+        shapes.append(shape.to_dict())
+    from_policy = []
+    for name in ref.list_packaged_gate0_seed_only_batched_policies():
+        policy = ref.load_packaged_gate0_seed_only_batched_policy(name)
+        if policy.kv_len_bucket is None or policy.heads is None or policy.kv_heads is None or policy.dim is None:
+            continue
+        from_policy.append({"policy": name, "batch": None,
+                            "shape": ref.seed_shape_from_policy(policy).to_dict()})
+        from_policy.append({"policy": name, "batch": 3,
+                            "shape": ref.seed_shape_from_policy(policy, batch=3, dtype_bytes=4).to_dict()})
+    payload = {"bucket_decisions": decisions, "seed_shapes": shapes, "seed_shapes_from_policy": from_policy}
+    (HERE / "route_policy.json").write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n")
+
+
 def rope_append_goldens(ref_root: Path) -> None:
     """RoPE + append through the reference's own safe path (`_apply_qwen_rope` + `copy_`,
     benchmarks/profile_seed_only_fused_rope_parity.py:24-30, 97-102), on CPU tensors."""
@@ -354,6 +390,7 @@ def main() -> None:
     paged_goldens(ref)
     seed_goldens(ref, ref_root)
     host_contract_goldens(ref)
+    route_policy_goldens(ref)
     rope_append_goldens(ref_root)
     print("fixtures written to", HERE)
 

@@ -1,6 +1,6 @@
 """Condense a StreamAttn checkout's seed-only policy artifacts into ``seed_only_cells.json``.
 
-    python -m streamattn_b200.policies.make_cells /path/to/StreamAttn/stream_attention/policies
+    python tests/golden/make_policy_cells.py /path/to/StreamAttn/stream_attention/policies
 
 Each registry entry of the checkout becomes one cell: the registry metadata used
 for discovery plus the policy fields this package's loader
@@ -17,7 +17,10 @@ import sys
 from dataclasses import asdict
 from pathlib import Path
 
-from ..decode import Gate0SeedOnlyBatchedPolicy
+ROOT = Path(__file__).resolve().parents[2]  # repository root
+sys.path.insert(0, str(ROOT))
+
+from streamattn_b200.decode import Gate0SeedOnlyBatchedPolicy  # noqa: E402
 
 REGISTRY_KEYS = ("name", "policy_id", "aliases", "status", "model_id", "layer_id", "mode", "tensor_space",
                  "dtype", "kv_len_bucket", "min_batch", "q_heads", "kv_heads", "head_dim", "attention_type")
@@ -39,7 +42,7 @@ def main(argv) -> None:
         "default": registry.get("default"),
         "cells": cells,
     }
-    out = Path(__file__).resolve().parent / "seed_only_cells.json"
+    out = ROOT / "streamattn_b200" / "policies" / "seed_only_cells.json"
     out.write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n", encoding="utf-8")
     print(f"wrote {len(cells)} cells to {out}")
 

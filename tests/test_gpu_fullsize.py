@@ -1,10 +1,11 @@
 """Full-size configurations of the benchmark, checked on the GPU.
 
-The CPU oracle would need minutes at these sizes, so the checks are a float32
-torch reference evaluated on the same GPU (plain PyTorch, the reference's own
-formula) plus size-independent properties of exact attention: invariance to the
-split count, linearity in V, and shard states merging to the unsharded result.
-Tolerance: max-abs 2e-2, mean-abs 2e-3 (bf16 outputs vs fp32).
+The CPU oracle would need minutes for a whole configuration at these sizes, so every
+configuration is checked three ways: (1) the pinned C oracle (``oracle/sa_oracle.c``, double
+accumulation) on two full-length (row, KV head) pairs - seconds of CPU each; (2) all rows
+against a float32 torch formula evaluated on the same GPU; (3) size-independent properties of
+exact attention: invariance to the split count, linearity in V, and shard states merging to the
+unsharded result.  Tolerance: max-abs 2e-2, mean-abs 2e-3 (bf16 outputs vs fp32).
 """
 
 from __future__ import annotations
@@ -15,6 +16,7 @@ import pytest
 import torch
 
 import streamattn_b200 as sa
+from oracle import cpu_oracle
 from streamattn_b200 import native
 
 pytestmark = pytest.mark.gpu
@@ -52,6 +54,19 @@ def torch_reference(q, k_bhnd, v_bhnd, lengths=None):
     return out
 
 
+def oracle_pairs(out, q, k_bhnd, v_bhnd, pairs, lengths=None):
+    """Compare the kernel's output rows of the given (row, kv head) pairs with the C oracle."""
+
+    group = q.shape[2] // k_bhnd.shape[1]
+    for b, h in pairs:
+        n = int(lengths[b]) if lengths is not None else k_bhnd.shape[2]
+        heads = slice(h * group, (h + 1) * group)
+        want = cpu_oracle.exact_decode(q[b:b + 1, :, heads].float().cpu(), k_bhnd[b:b + 1, h:h + 1, :n].float().cpu(),
+                                       v_bhnd[b:b + 1, h:h + 1, :n].float().cpu(), kv_layout="BHND")
+        diff = (out[b:b + 1, :, heads].float().cpu() - want).abs()
+        assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS, (b, h, float(diff.max()))
+
+
 def _randn(shape, seed, dev):
     g = torch.Generator(device=dev).manual_seed(seed)
     return torch.randn(shape, generator=g, device=dev, dtype=torch.float32).bfloat16()
@@ -68,6 +83,7 @@ def test_config2_exact_contiguous_b8_n65536(dev):
     out = plan.run().clone()
     assert plan.device_status() == 0
     _close(out, want)
+    oracle_pairs(out, q, k, v, [(0, 0), (batch - 1, kv_heads - 1)])
     assert torch.equal(plan.run(), out)                             # deterministic replay
     # BNHD view of the same values gives the same answer.
     kb, vb = k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous()
@@ -125,6 +141,8 @@ def test_config3_paged_page16_ragged(dev):
         kc[b, :, : active * page] = k[ids].permute(1, 0, 2, 3).reshape(kv_heads, active * page, dim)
         vc[b, :, : active * page] = v[ids].permute(1, 0, 2, 3).reshape(kv_heads, active * page, dim)
     _close(out, torch_reference(q, kc, vc, lengths))
+    shortest, longest = int(lengths.argmin()), int(lengths.argmax())
+    oracle_pairs(out, q, kc, vc, [(shortest, 0), (longest, kv_heads - 1)], lengths)
     # Bit-exact page walk: every active slot visited with its own physical page, -1 slots untouched.
     assert torch.equal(plan.trace.cpu(), table)
     # Dynamic schedule: within tolerance on every launch, same page walk.
@@ -158,6 +176,7 @@ def test_config4_seed_only_qwen_shape(dev):
     ks = k.index_select(1, tokens).transpose(1, 2)
     vs = v.index_select(1, tokens).transpose(1, 2)
     _close(out, torch_reference(q, ks, vs))
+    oracle_pairs(out, q, ks, vs, [(0, 0), (batch - 1, kv_heads - 1)])
     assert info.stats["seed_blocks"] == 12 and info.stats["total_blocks"] == 1024
 
 
@@ -169,7 +188,9 @@ def test_config5_shape_family_d128_g4_long_context(dev):
     k = _randn((1, kv_heads, kv_len, dim), 10, dev)
     v = _randn((1, kv_heads, kv_len, dim), 11, dev)
     want = torch_reference(q, k, v)
-    _close(sa.ExactDecodePlan.build(q, k, v).run(), want)
+    whole = sa.ExactDecodePlan.build(q, k, v).run()
+    _close(whole, want)
+    oracle_pairs(whole, q, k, v, [(0, 0), (0, kv_heads - 1)])
     from streamattn_b200.context_parallel import shard_bounds
 
     states = []

@@ -326,3 +326,39 @@ def test_kv_layout_inference_matches_the_reference_gate():
     assert layout((8, 1, 16, 64), (8, 2, 65536, 64), torch.float16) == "BNHD"
     assert layout((3, 1, 16, 64), (3, 2, 65536, 64)) == "BNHD"
     assert layout((1, 1, 16, 64), (1, 4, 65536, 64)) == "BNHD"
+
+
+def test_seed_only_launcher_failure_falls_closed_to_exact_with_the_reason(monkeypatch):
+    """A seed-only launch that raises must not reach the caller when the policy's fallback is
+    dense: the service runs exact instead and records ``seed_only_batched_backend_error:<Exc>``
+    (reference decode.py:2573-2591; its tests/test_decode_plan.py:649, 1126).  The failure is
+    made on the host - the launcher is replaced by one that raises - so no GPU is involved."""
+
+    q, k, v = _engine_inputs()
+    service = sa.StreamAttnSeedOnlyDecodeService(
+        policy=_test_policy(), decode_policy=sa.StreamAttnDecodePolicy(min_kv_len_for_gate0_seed_only=1),
+        dense_fallback=_zeros, use_planned_direct_seed_only_path=True)
+    monkeypatch.setattr(service, "_preflight_reasons", lambda *a, **kw: [])   # pretend the device qualifies
+
+    def broken_launcher(*args, **kwargs):
+        raise MemoryError("simulated launch failure")
+
+    monkeypatch.setattr(service, "_allocate_direct_runner", broken_launcher)
+    out, info = service.run(q, k, v, model_id="test-model", layer_id=3, mode="verified_auto")
+    assert torch.equal(out, torch.zeros_like(q))                               # the injected exact path
+    assert info.fallback_reason == "seed_only_batched_backend_error:MemoryError"
+    assert info.backend_used == sa.STREAMATTN_EXACT_NATIVE_BACKEND
+    assert info.runtime_counters["fallback_reasons"] == {"seed_only_batched_backend_error:MemoryError": 1}
+    assert info.seed_only_enabled is False
+    # Output only: the same fallback, no record.
+    assert torch.equal(service.run(q, k, v, model_id="test-model", layer_id=3, mode="auto", return_info=False),
+                       torch.zeros_like(q))
+    # A policy that forbids the dense fallback lets the error through.
+    strict = sa.StreamAttnSeedOnlyDecodeService(
+        policy=sa.Gate0SeedOnlyBatchedPolicy(**{**_test_policy().__dict__, "fallback": "error"}),
+        decode_policy=sa.StreamAttnDecodePolicy(min_kv_len_for_gate0_seed_only=1), dense_fallback=_zeros,
+        use_planned_direct_seed_only_path=True)
+    monkeypatch.setattr(strict, "_preflight_reasons", lambda *a, **kw: [])
+    monkeypatch.setattr(strict, "_allocate_direct_runner", broken_launcher)
+    with pytest.raises(MemoryError):
+        strict.run(q, k, v, model_id="test-model", layer_id=3, mode="verified_auto")

@@ -6,10 +6,8 @@ split-state workspace ``sa_exact_decode`` asks for.  The static variant keeps
 that scratch in a fixed 2 MiB array inside the library, so the caller passes
 inputs and outputs only.  Here it is called through the C ABI twice in a row
 (the array keeps the previous call's contents, so the second call proves the
-counters are re-armed) and compared with the workspace-taking entry point.
-
-This file is collected last on purpose: a run that stops at the first failure
-has then already executed every other test.
+counters are re-armed) and compared with the workspace-taking entry point;
+``sa_static_status`` must report a clean status word afterwards.
 """
 
 from __future__ import annotations
@@ -61,6 +59,8 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(name):
         assert torch.equal(got, expected), "same kernels, same schedule: results are bit-identical"
         ref = (got.float().cpu() - want).abs()
         assert float(ref.max()) <= 2e-2 and float(ref.mean()) <= 2e-3
+
+    assert native.static_status(dev) == 0, "no wait gave up, no bad page: the status word stays clean"
 
     # A different split count re-uses the same array with another slot layout.
     got = torch.empty_like(qd)
