@@ -12,6 +12,7 @@ Workloads (BASELINE.json configs):
   paged_c3   paged HND page-16, ragged lengths U[16384, 65536], random page order
   seed_c4    seed-only decode, Qwen2.5-3B attention shape, 384 seed tokens of 32768
   loop_c2    one decode-loop step on the config-2 cache: RoPE + KV append, then exact decode
+  o_proj_3b  the output projection that follows attention, Qwen2.5-3B shape (2048 x 2048 bf16 weights)
   cp_c5      context-parallel exact decode, B1 Hq32 Hkv8 D128 N1048576 sharded over N GPUs
              (strong scaling; state exchange fused into the decode kernel over peer memory) [default at N>1]
 
@@ -341,6 +342,21 @@ def build_seed_c4(device):
     return {"run": plan.run, "q": q, "out": out, "info": info, "plan": plan, "rebind": bind}
 
 
+def build_o_proj_3b(device):
+    """The output projection that follows attention in Qwen2.5-3B: [8, 1, 2048] x [2048, 2048]^T, bf16."""
+
+    import streamattn_b200 as sa
+
+    B, heads, dim, hidden = 8, 16, 128, 2048
+    attn = _randn_bf16((B, 1, heads, dim), 80, device)
+    weight = (_randn_bf16((hidden, heads * dim), 81, device).float() / 16.0).bfloat16()
+    plan = sa.OProjPlan.build(attn.view(B, 1, heads * dim), weight)
+    info = dict(workload="o_proj_3b", batch=B, in_features=heads * dim, out_features=hidden,
+                kernel="sm100_o_proj_weight_stream", ctas=hidden // 8, bytes=hidden * heads * dim * 2 + 2 * B * hidden * 2,
+                launches=1, l2="the 8 MB of weights stay L2-resident between back-to-back calls")
+    return {"run": plan.run, "q": attn, "out": plan.output, "info": info, "plan": plan}
+
+
 def build_cp_c5(device, rank, world, exchange="auto", kv_len=1048576):
     from streamattn_b200.context_parallel import ContextParallelExactDecode, shard_bounds
 
@@ -612,6 +628,98 @@ def cpu_baseline_sample(workload: str, steps: int = 3, warmup: int = 1, budget_s
             "ms_per_sample": dt * 1e3, "samples_timed": done}
 
 
+def quick_time(fn, device, iters: int = 200, repeats: int = 5, warmup: int = 20) -> float:
+    """Median microseconds per call over ``repeats`` event-timed regions of ``iters`` calls."""
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    return statistics.median(time_region(fn, iters, device) / iters * 1e6 for _ in range(repeats))
+
+
+def measure_seed_grid(device) -> dict:
+    """Seed-only decode at batch 1-8 x 128-1024 seed tokens (Qwen2.5-3B attention shape): the grid
+    the latency model picks (``seed_autotune``) against a sweep of CTAs per (row, KV head) pair."""
+
+    from streamattn_b200 import native
+    from streamattn_b200.seed_autotune import SeedKernelShape, autotune_seed_kernel_mode
+
+    Hq, Hkv, D, N, bs = 16, 2, 128, 32768, 32
+    cells, worst = [], 0.0
+    for B in (1, 2, 4, 8):
+        q = _randn_bf16((B, 1, Hq, D), 40 + B, device)
+        k = _randn_bf16((B, N, Hkv, D), 50 + B, device)
+        v = _randn_bf16((B, N, Hkv, D), 60 + B, device)
+        out = torch.empty_like(q)
+        pairs = B * Hkv
+        for S in (128, 384, 1024):
+            nb = S // bs
+            blocks = list(range(nb // 2)) + list(range(N // bs - (nb - nb // 2), N // bs))
+            shape = SeedKernelShape(batch=B, q_heads=Hq, kv_heads=Hkv, kv_len=N, dim=D, block_size=bs,
+                                    sink_blocks=nb, recent_blocks=0, middle_seed_blocks=0)
+            pick = autotune_seed_kernel_mode(shape, sm_count=native.sm_count(device))
+            swept = {}
+            for chunks in sorted({1, 2, 3, 4, 6, 8, 12, pick.recommended_num_ctas // pairs}):
+                ctas = chunks * pairs
+                if chunks > shape.tiles_per_pair or ctas > 148:
+                    continue
+                ws = native.new_workspace(device, B, Hq, Hkv, D, ctas)
+                plan = native.seed_plan(q, k, v, out, ws, block_size=bs, blocks=blocks, num_ctas=ctas)
+                swept[ctas] = quick_time(plan.run, device)
+            best_ctas = min(swept, key=swept.get)
+            chosen_us = swept[pick.recommended_num_ctas]
+            loss = chosen_us / swept[best_ctas] - 1.0
+            worst = max(worst, loss)
+            cells.append({"batch": B, "seed_tokens": S, "chosen_ctas": pick.recommended_num_ctas,
+                          "chosen_us": chosen_us, "predicted_us": pick.predicted_us, "best_ctas": best_ctas,
+                          "best_us": swept[best_ctas], "chosen_over_best": 1.0 + loss,
+                          "swept_us_by_ctas": {str(c): t for c, t in swept.items()}})
+        del q, k, v
+    return {"workload": "seed_grid", "shape": "Hq16 Hkv2 D128 N32768 bf16, block 32, sink+recent blocks",
+            "l2": "seed sets stay L2-resident between back-to-back calls", "timing": "median of 5 x 200 calls",
+            "worst_chosen_over_best": 1.0 + worst, "cells": cells}
+
+
+def measure_o_proj(device) -> dict:
+    """The output projection that follows attention (Qwen2.5-3B: 2048 -> 2048, bf16, 8 MB of weights):
+    alone, with L2 flushed, and chained behind the seed-only decode of the config-4 shape."""
+
+    import streamattn_b200 as sa
+
+    case = build_seed_c4(device)
+    B, hidden = 8, 2048
+    weight = (_randn_bf16((hidden, hidden), 70, device).float() / 16.0).bfloat16()
+    proj = sa.OProjPlan.build(case["out"].view(B, 1, hidden), weight)
+    late = sa.OProjPlan.build(case["out"].view(B, 1, hidden), weight, prefetch_weights=False)
+    decode = case["run"]
+
+    def chain():
+        decode()
+        return proj.run()
+
+    def chain_late():
+        decode()
+        return late.run()
+
+    alg = hidden * hidden * 2 + 2 * B * hidden * 2
+    peak, peak_kind = measured_hbm_peak()
+    alone = quick_time(proj.run, device)
+    cold = cold_time(proj.run, device)
+    decode_us = quick_time(decode, device)
+    chain_us = quick_time(chain, device)
+    chain_late_us = quick_time(chain_late, device)
+    cold_gbs = alg / (cold["us_per_call"] * 1e-6) / 1e9
+    return {"workload": "o_proj_qwen3b", "batch": B, "in_features": hidden, "out_features": hidden,
+            "algorithmic_bytes": alg, "us_per_call_l2_warm": alone, "cold_l2": cold,
+            "roofline_cold": {"bound": "hbm", "achieved": cold_gbs, "peak": peak, "unit": "GB/s",
+                              "frac": cold_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth",
+                              "note": "8 MB per launch: launch latency, not bandwidth, dominates"},
+            "seed_decode_us": decode_us, "seed_decode_then_o_proj_us": chain_us,
+            "o_proj_visible_us": chain_us - decode_us,
+            "seed_decode_then_o_proj_no_weight_prefetch_us": chain_late_us,
+            "timing": "median of 5 x 200 calls; chain = two launches per step on one stream"}
+
+
 BUILDERS = {
     "exact_c2": lambda device: build_exact_c2(device),
     "exact_c2_bnhd": lambda device: build_exact_c2(device, "BNHD"),
@@ -619,6 +727,7 @@ BUILDERS = {
     "seed_c4": build_seed_c4,
     "loop_c2": build_loop_c2,
     "cp_c5_1gpu": lambda device: build_cp_c5_single(device),
+    "o_proj_3b": build_o_proj_3b,
 }
 SECONDARY = ("paged_c3", "seed_c4", "exact_c2_bnhd", "loop_c2", "cp_c5_1gpu")
 
@@ -653,7 +762,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "exact_c2", "exact_c2_bnhd", "paged_c3", "seed_c4", "loop_c2", "cp_c5",
-                             "cp_c5_1gpu"])
+                             "cp_c5_1gpu", "o_proj_3b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true",
                     help="N=1: only the headline workload (the other configurations are skipped)")
@@ -789,9 +898,14 @@ def main() -> None:
             secondary.append(entry)
             del other
             torch.cuda.empty_cache()
+    extras = []
+    if world == 1 and workload == "exact_c2" and not args.no_secondary:
+        extras = [measure_seed_grid(device), measure_o_proj(device)]
+        torch.cuda.empty_cache()
     clocks.stop()
     for entry in [head, *secondary]:
         entry["clocks"] = clocks.summary(*entry.pop("clock_window"))
+    secondary.extend(extras)
 
     if rank == 0:
         value = alg_bytes / step_s / 1e9

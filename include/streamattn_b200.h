@@ -231,6 +231,49 @@ SA_API int sa_seed_decode_blocks(const void *q, const void *k, const void *v, vo
                                  int num_ctas, int kernel_choice, sa_stream_t stream);
 
 /*
+ * Run-time seed selection: the middle seed blocks of every (row, KV head) pair are chosen by
+ * scoring the K cache against the current query instead of taking fixed positions.  All three
+ * steps stay on the device; the block list never visits the host.
+ * Replaces _score_tensor_for_runtime_selector and select_seed_blocks_by_profile
+ * (seed_selectors.py:274-396) for the selectors that need only q and K:
+ *   SA_SELECT_QK_BLOCK_MAX  score = max over the block's tokens of q.k   ("qk_block_max")
+ *   SA_SELECT_BLOCK_MEAN    score = q . mean key of the block            ("block_mean_proxy")
+ *
+ * sa_block_scores: scores[batch, q_heads, ceil(kv_len / block_size)] f32 (device), one score
+ *   per query head as in the reference; blocks without valid tokens get -inf.  bf16/fp16.
+ * sa_seed_list_length: entries per pair of the lists below: min(blocks of the cache,
+ *   sink + recent (de-duplicated) + middle).
+ * sa_select_seed_blocks: blocks_out[batch * kv_heads, list_length] int32 (device), ascending.
+ *   A pair's block score is the maximum over the query heads that share the KV head; sink and
+ *   recent blocks are always kept; the best `middle_seed_blocks` other blocks join them (ties:
+ *   lower index), the policy's fixed middle blocks filling up if too few blocks have a score.
+ * sa_seed_plan_create_device: seed-only decode plan that reads each pair's block list from
+ *   `blocks_dev` (as written by sa_select_seed_blocks) at run time; includes_last_block != 0
+ *   says that every list ends with the cache's last block (true whenever recent_blocks >= 1),
+ *   which is how a partly filled last block is accounted for.  Entries outside the cache are
+ *   skipped and reported as SA_DEV_BAD_PAGE.
+ */
+enum sa_block_selector { SA_SELECT_QK_BLOCK_MAX = 0, SA_SELECT_BLOCK_MEAN = 1 };
+SA_API int sa_block_scores(const void *q, const void *k, float *scores, const void *seq_lens, int lens_dtype,
+                           int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                           int64_t q_stride_b, int64_t q_stride_h,
+                           int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                           int dtype, int block_size, int selector, sa_stream_t stream);
+SA_API int sa_seed_list_length(int64_t kv_len, int block_size, int sink_blocks, int recent_blocks,
+                               int middle_seed_blocks);
+SA_API int sa_select_seed_blocks(const float *scores, int32_t *blocks_out, int batch, int q_heads, int kv_heads,
+                                 int64_t kv_len, int block_size, int sink_blocks, int recent_blocks,
+                                 int middle_seed_blocks, int block_order, sa_stream_t stream);
+SA_API sa_plan_t *sa_seed_plan_create_device(const void *q, const void *k, const void *v, void *out,
+                                             void *workspace, size_t workspace_bytes,
+                                             int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                                             int64_t q_stride_b, int64_t q_stride_h,
+                                             int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                             int dtype, int block_size, const int32_t *blocks_dev,
+                                             int blocks_per_pair, int includes_last_block,
+                                             int num_ctas, int kernel_choice);
+
+/*
  * Exact merge of split states: states [num_parts, rows, D+2] f32 (layout of
  * SA_OUT_STATE) -> out [rows, D] in out_dtype.  Used after the cross-GPU
  * gather of context-parallel decode.  Same arithmetic as

@@ -203,3 +203,61 @@ def o_proj(attn_output: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
     w = weight.detach().to("cpu", torch.float32)
     b = None if bias is None else bias.detach().to("cpu", torch.float32)
     return torch.nn.functional.linear(x, w, b)
+
+
+def block_scores(q: torch.Tensor, k: torch.Tensor, *, block_size: int, selector: str) -> torch.Tensor:
+    """Score of every block of one head's keys against one query, float32 on the CPU.
+
+    ``q`` is ``[D]``, ``k`` is ``[N, D]``.  Restates the reference's run-time selectors
+    (seed_selectors.py:174-196 blocked view and ``qk_block_max``, :252-259 ``block_mean_proxy``):
+    the cache is cut into blocks of ``block_size`` tokens (the last one may be short); a block's
+    score is the largest q.k over its tokens, or q dotted with the mean of its keys.
+    """
+
+    q = q.detach().to("cpu", torch.float32)
+    k = k.detach().to("cpu", torch.float32)
+    n = int(k.shape[0])
+    scores = []
+    for start in range(0, n, int(block_size)):
+        block = k[start:min(n, start + int(block_size))]
+        if selector == "qk_block_max":
+            scores.append(torch.matmul(block, q).max())
+        elif selector == "block_mean_proxy":
+            scores.append(torch.dot(block.mean(dim=0), q))
+        else:
+            raise ValueError(f"selector {selector!r} is not restated here")
+    return torch.stack(scores)
+
+
+def select_blocks(scores: torch.Tensor, *, seq_len: int, block_size: int, sink_blocks: int, recent_blocks: int,
+                  middle_seed_blocks: int, block_order: str) -> List[int]:
+    """Seed blocks chosen from block scores (ascending list).
+
+    ``scores`` is ``[heads_sharing_the_kv_head, num_blocks]``: a block's score is the maximum
+    over those heads (one head: the reference's per-head rule, seed_selectors.py:347-384).  Sink
+    and recent blocks are always kept; the ``middle_seed_blocks`` best other blocks join them,
+    ordered by (-score, index), non-finite scores never selecting; the policy's fixed middle
+    blocks fill up if fewer blocks have a score.
+    """
+
+    num_blocks = math.ceil(int(seq_len) / int(block_size))
+    recent_start = num_blocks - int(recent_blocks)
+    base = [b for b in range(min(int(sink_blocks), num_blocks))]
+    base += [b for b in range(max(recent_start, 0), num_blocks) if b not in base]
+    pair = scores.detach().to("cpu", torch.float32).reshape(-1, num_blocks)
+    pair = torch.where(torch.isfinite(pair), pair, torch.full_like(pair, -float("inf"))).max(dim=0).values
+    ranked = sorted(range(num_blocks), key=lambda b: (-float(pair[b]), b))
+    middle: List[int] = []
+    for b in ranked:
+        if len(middle) >= int(middle_seed_blocks):
+            break
+        if b in base or not math.isfinite(float(pair[b])):
+            continue
+        middle.append(b)
+    for i in range(int(middle_seed_blocks)):
+        if len(middle) >= int(middle_seed_blocks):
+            break
+        b = int(sink_blocks) + i if block_order == "sequential" else recent_start - 1 - i
+        if 0 <= b < num_blocks and b not in base and b not in middle:
+            middle.append(b)
+    return sorted(base + middle)

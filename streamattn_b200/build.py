@@ -17,7 +17,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC_DIR = PACKAGE_DIR / "csrc"
 LIB_DIR = PACKAGE_DIR / "_lib"
 LIB_PATH = LIB_DIR / "libstreamattn_b200.so"
-SOURCES = ("sa_api.cu", "sa_generic.cu", "sa_stream.cu", "sa_exchange.cu", "sa_append.cu", "sa_oproj.cu")
+SOURCES = ("sa_api.cu", "sa_generic.cu", "sa_stream.cu", "sa_exchange.cu", "sa_append.cu", "sa_oproj.cu", "sa_select.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",

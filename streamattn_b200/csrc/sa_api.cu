@@ -421,6 +421,41 @@ int fill_seed(sa_plan *plan, const void *q, const void *k, const void *v, void *
     return finish_plan(plan, workspace, workspace_bytes, vlen, kernel_choice);
 }
 
+
+int fill_seed_device(sa_plan *plan, const void *q, const void *k, const void *v, void *out, void *workspace,
+                     size_t workspace_bytes, int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len,
+                     int64_t q_sb, int64_t q_sh, int64_t kv_sb, int64_t kv_sn, int64_t kv_sh, int dtype, int block_size,
+                     const int32_t *blocks_dev, int blocks_per_pair, int includes_last_block, int num_ctas,
+                     int kernel_choice)
+{
+    int rc = check_common(q, k, v, out, workspace, batch, q_heads, kv_heads, head_dim, dtype, SA_OUT_FINAL, num_ctas,
+                          kernel_choice);
+    if (rc) return rc;
+    if (kv_len <= 0 || block_size <= 0) return fail(SA_ERR_INVALID, "kv_len and block_size must be positive");
+    if (!blocks_dev || blocks_per_pair <= 0) return fail(SA_ERR_INVALID, "a device block list with at least one block per pair is required");
+    const int64_t cache_blocks = (kv_len + block_size - 1) / block_size;
+    if (blocks_per_pair > cache_blocks) return fail(SA_ERR_INVALID, "more seed blocks per pair than the cache has blocks");
+    std::memset(plan, 0, sizeof(*plan));
+    Problem &p = plan->problem;
+    p.q = q; p.k = k; p.v = v; p.out = out;
+    p.dtype = dtype; p.out_mode = SA_OUT_FINAL;
+    p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.q_sb = q_sb; p.q_sh = q_sh;
+    p.seq.mode = kBlocks;
+    p.seq.num_rows = -1;
+    p.seq.kv_sb = kv_sb; p.seq.kv_sn = kv_sn; p.seq.kv_sh = kv_sh;
+    p.seq.kv_len = kv_len;
+    p.seq.block_size = block_size;
+    p.seq.num_blocks = blocks_per_pair;
+    p.seq.blocks_dev = blocks_dev;
+    p.seq.blocks_kv_heads = kv_heads;
+    // Lists are ascending, so only a pair's last entry can be the cache's (possibly short) last block.
+    const int64_t clip = includes_last_block && kv_len % block_size ? block_size - kv_len % block_size : 0;
+    p.seq.blocks_vlen = static_cast<int64_t>(blocks_per_pair) * block_size - clip;
+    p.num_ctas = num_ctas;
+    return finish_plan(plan, workspace, workspace_bytes, p.seq.blocks_vlen, kernel_choice);
+}
+
 }  // namespace
 }  // namespace sa
 
@@ -641,6 +676,82 @@ int sa_seed_decode(const void *q, const void *k, const void *v, void *out, void 
     return sa_seed_decode_blocks(q, k, v, out, workspace, workspace_bytes, batch, q_heads, kv_heads, head_dim, kv_len,
                                  q_stride_b, q_stride_h, kv_stride_b, kv_stride_n, kv_stride_h, dtype, block_size,
                                  blocks, n, num_ctas, kernel_choice, stream);
+}
+
+sa_plan_t *sa_seed_plan_create_device(const void *q, const void *k, const void *v, void *out, void *workspace,
+                                      size_t workspace_bytes, int batch, int q_heads, int kv_heads, int head_dim,
+                                      int64_t kv_len, int64_t q_stride_b, int64_t q_stride_h, int64_t kv_stride_b,
+                                      int64_t kv_stride_n, int64_t kv_stride_h, int dtype, int block_size,
+                                      const int32_t *blocks_dev, int blocks_per_pair, int includes_last_block,
+                                      int num_ctas, int kernel_choice)
+{
+    sa_plan *plan = new (std::nothrow) sa_plan;
+    if (!plan) return nullptr;
+    if (fill_seed_device(plan, q, k, v, out, workspace, workspace_bytes, batch, q_heads, kv_heads, head_dim, kv_len,
+                         q_stride_b, q_stride_h, kv_stride_b, kv_stride_n, kv_stride_h, dtype, block_size, blocks_dev,
+                         blocks_per_pair, includes_last_block, num_ctas, kernel_choice)) {
+        delete plan;
+        return nullptr;
+    }
+    return plan;
+}
+
+int sa_block_scores(const void *q, const void *k, float *scores, const void *seq_lens, int lens_dtype, int batch,
+                    int q_heads, int kv_heads, int head_dim, int64_t kv_len, int64_t q_stride_b, int64_t q_stride_h,
+                    int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h, int dtype, int block_size,
+                    int selector, sa_stream_t stream)
+{
+    if (!q || !k || !scores) return fail(SA_ERR_INVALID, "sa_block_scores: null tensor pointer");
+    if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads)
+        return fail(SA_ERR_INVALID, "sa_block_scores: bad batch / head counts");
+    if (kv_len <= 0 || block_size <= 0) return fail(SA_ERR_INVALID, "sa_block_scores: kv_len and block_size must be positive");
+    if (dtype != SA_DTYPE_BF16 && dtype != SA_DTYPE_F16) return fail(SA_ERR_UNSUPPORTED, "sa_block_scores: dtype must be bf16 or fp16");
+    if (selector != SA_SELECT_QK_BLOCK_MAX && selector != SA_SELECT_BLOCK_MEAN)
+        return fail(SA_ERR_INVALID, "sa_block_scores: unknown selector");
+    if (q_heads / kv_heads > 16) return fail(SA_ERR_UNSUPPORTED, "sa_block_scores: more than 16 query heads per KV head");
+    if (head_dim <= 0 || head_dim > 256 || head_dim % 8 || kv_stride_n % 8 || kv_stride_h % 8 || kv_stride_b % 8 ||
+        reinterpret_cast<uintptr_t>(k) % 16)
+        return fail(SA_ERR_UNSUPPORTED, "sa_block_scores: head_dim and the KV strides must be multiples of 8 (16-byte rows)");
+    if (lens_dtype != SA_INDEX_I32 && lens_dtype != SA_INDEX_I64) return fail(SA_ERR_INVALID, "unknown lens_dtype");
+    if ((kv_len + block_size - 1) / block_size > (1 << 24)) return fail(SA_ERR_UNSUPPORTED, "sa_block_scores: too many blocks");
+    const cudaError_t err = launch_block_scores(q, k, scores, seq_lens, lens_dtype == SA_INDEX_I64, batch, q_heads,
+                                                kv_heads, head_dim, kv_len, q_stride_b, q_stride_h, kv_stride_b,
+                                                kv_stride_n, kv_stride_h, dtype, block_size, selector,
+                                                static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_block_scores");
+    return SA_OK;
+}
+
+int sa_seed_list_length(int64_t kv_len, int block_size, int sink_blocks, int recent_blocks, int middle_seed_blocks)
+{
+    if (kv_len <= 0 || block_size <= 0 || sink_blocks < 0 || recent_blocks < 0 || middle_seed_blocks < 0) {
+        fail(SA_ERR_INVALID, "sa_seed_list_length: bad argument");
+        return -1;
+    }
+    const int64_t nb = (kv_len + block_size - 1) / block_size;
+    const int64_t base = std::min<int64_t>(nb, std::min<int64_t>(sink_blocks, nb) + std::min<int64_t>(recent_blocks, nb));
+    return static_cast<int>(std::min<int64_t>(nb, base + middle_seed_blocks));
+}
+
+int sa_select_seed_blocks(const float *scores, int32_t *blocks_out, int batch, int q_heads, int kv_heads,
+                          int64_t kv_len, int block_size, int sink_blocks, int recent_blocks, int middle_seed_blocks,
+                          int block_order, sa_stream_t stream)
+{
+    if (!scores || !blocks_out) return fail(SA_ERR_INVALID, "sa_select_seed_blocks: null tensor pointer");
+    if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads)
+        return fail(SA_ERR_INVALID, "sa_select_seed_blocks: bad batch / head counts");
+    if (block_order < SA_ORDER_SEQUENTIAL || block_order > SA_ORDER_SINK_RECENT_FIRST)
+        return fail(SA_ERR_INVALID, "sa_select_seed_blocks: unknown block_order");
+    const int list_len = sa_seed_list_length(kv_len, block_size, sink_blocks, recent_blocks, middle_seed_blocks);
+    if (list_len <= 0) return fail(SA_ERR_INVALID, "sa_select_seed_blocks: the policy selects no block");
+    if (list_len > SA_MAX_SEED_BLOCKS) return fail(SA_ERR_UNSUPPORTED, "more than %d seed blocks", SA_MAX_SEED_BLOCKS);
+    const int64_t nb = (kv_len + block_size - 1) / block_size;
+    if (nb * 4 > 200 * 1024) return fail(SA_ERR_UNSUPPORTED, "sa_select_seed_blocks: more than 51200 blocks per row");
+    const cudaError_t err = launch_select_blocks(scores, blocks_out, batch, q_heads, kv_heads, static_cast<int>(nb),
+                                                 sink_blocks, recent_blocks, middle_seed_blocks, block_order, list_len,
+                                                 static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "sa_select_seed_blocks");
+    return SA_OK;
 }
 
 int sa_merge_states(const float *states, int num_parts, int64_t rows, int head_dim, void *out, int out_dtype,

@@ -46,10 +46,14 @@ struct SeqDesc {
     int page_size;
     int64_t num_pages;
     int64_t pg_sp, pg_st, pg_sh;
-    // seed blocks (ascending, unique)
+    // seed blocks (ascending, unique): one list for the whole call (`blocks`), or - when
+    // blocks_dev is set - one device-resident list of num_blocks entries per (row, kv head) pair,
+    // pair = row * blocks_kv_heads + kv head
     int block_size;
     int num_blocks;
     int64_t blocks_vlen;  // number of valid virtual tokens of the block list
+    const int32_t *blocks_dev;
+    int blocks_kv_heads;
     int32_t blocks[kMaxSeedBlocks];
 };
 
@@ -153,6 +157,14 @@ size_t exchange_status_offset(int world, int64_t rows, int dim);
 cudaError_t launch_exchange_merge(const float *local_state, const uint64_t *bases_host, int world, int rank,
                                   uint32_t step, int64_t rows, int dim, void *out, int out_dtype,
                                   unsigned long long wait_ns, cudaStream_t stream);
+
+cudaError_t launch_block_scores(const void *q, const void *k, float *scores, const void *seq_lens, int lens_i64,
+                                int batch, int q_heads, int kv_heads, int head_dim, int64_t kv_len, int64_t q_sb,
+                                int64_t q_sh, int64_t kv_sb, int64_t kv_sn, int64_t kv_sh, int dtype, int block_size,
+                                int selector, cudaStream_t stream);
+cudaError_t launch_select_blocks(const float *scores, int32_t *blocks_out, int batch, int q_heads, int kv_heads,
+                                 int num_blocks, int sink_blocks, int recent_blocks, int middle_blocks,
+                                 int block_order, int list_len, cudaStream_t stream);
 
 cudaError_t launch_o_proj(const void *x, const void *w, const void *bias, void *out, int batch, int in_features,
                           int out_features, int64_t x_stride, int dtype, int prefetch_weights, cudaStream_t stream);

@@ -36,7 +36,13 @@ __device__ inline int64_t token_offset(const SeqDesc &s, int b, int kvh, int64_t
 {
     if (s.mode == kContig) return b * s.kv_sb + t * s.kv_sn + kvh * s.kv_sh;
     if (s.mode == kBlocks) {
-        int64_t tok = static_cast<int64_t>(s.blocks[t / s.block_size]) * s.block_size + t % s.block_size;
+        const int64_t bi = t / s.block_size;
+        const int64_t blk = s.blocks_dev != nullptr
+                                ? s.blocks_dev[(static_cast<int64_t>(b) * s.blocks_kv_heads + kvh) * s.num_blocks + bi]
+                                : s.blocks[bi];
+        const int64_t tok = blk * s.block_size + t % s.block_size;
+        *page_out = blk;
+        if (blk < 0 || tok >= s.kv_len) return -1;  // device lists are not host-checked: skip and report
         return b * s.kv_sb + tok * s.kv_sn + kvh * s.kv_sh;
     }
     int64_t lp = t / s.page_size;

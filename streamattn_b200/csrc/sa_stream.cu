@@ -851,9 +851,17 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         } else {
             const unsigned bi = vfrag >> p.fpu_shift;
             const int sub = static_cast<int>(vfrag - (bi << p.fpu_shift));
-            f.tok = p.seq.blocks[bi] * p.seq.block_size + (sub << p.frag_shift);
+            int blk;
+            if (p.seq.blocks_dev != nullptr) {  // the pair's own list, written by a kernel before this one
+                const int64_t pair = static_cast<int64_t>(pc_b) * p.seq.blocks_kv_heads + f.kvh;
+                blk = p.seq.blocks_dev[pair * p.seq.num_blocks + bi];
+            } else {
+                blk = p.seq.blocks[bi];
+            }
+            f.tok = blk * p.seq.block_size + (sub << p.frag_shift);
             f.outer = pc_b;
-            f.state = 1;
+            // A device list cannot be checked by the host: blocks outside the cache are skipped and reported.
+            f.state = (blk >= 0 && static_cast<int64_t>(f.tok) < p.seq.kv_len) ? 1 : 2;
         }
         return f;
     };

@@ -69,6 +69,10 @@ _SIGNATURES = {
     "sa_seed_decode": (_SEED_COMMON + [_i, _i, _i, _i, _i, _i, _i, _vp], _i),
     "sa_seed_decode_blocks": (_SEED_COMMON + [_i, _i32p, _i, _i, _i, _vp], _i),
     "sa_merge_states": ([_vp, _i, _i64, _i, _vp, _i, _vp], _i),
+    "sa_block_scores": ([_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp], _i),
+    "sa_seed_list_length": ([_i64, _i, _i, _i, _i], _i),
+    "sa_select_seed_blocks": ([_vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _i, _i, _vp], _i),
+    "sa_seed_plan_create_device": (_SEED_COMMON + [_i, _vp, _i, _i, _i, _i], _vp),
     "sa_cp_exchange_bytes": ([_i, _i64, _i], _sz),
     "sa_cp_exchange_merge": ([_vp, ctypes.POINTER(ctypes.c_uint64), _i, _i, ctypes.c_uint32, _i64, _i, _vp, _i, _vp], _i),
     "sa_cp_exchange_status": ([_vp, _i, _i64, _i, _vp], _i),
@@ -494,6 +498,99 @@ def seed_plan(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, outpu
             int(block_size), arr, nb, int(num_ctas), SA_KERNEL[kernel],
         )
     return NativePlan(handle, device, (query, key, value, output, workspace))
+
+
+SA_SELECTOR = {"qk_block_max": 0, "block_mean_proxy": 1}
+
+
+def block_scores(query: torch.Tensor, key: torch.Tensor, *, block_size: int, selector: str,
+                 kv_layout: str = "BNHD", seq_lens: Optional[torch.Tensor] = None,
+                 scores: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``scores[B, Hq, ceil(N / block_size)]`` (float32) of every cache block against the query."""
+
+    device = require_cuda(query, key, seq_lens, scores)
+    if selector not in SA_SELECTOR:
+        raise ValueError(f"selector must be one of {sorted(SA_SELECTOR)}")
+    if query.dtype not in (torch.bfloat16, torch.float16) or key.dtype != query.dtype:
+        raise ValueError("query/key must share a dtype of bf16 or fp16")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, key, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    num_blocks = -(-kv_len // int(block_size))
+    if scores is None:
+        scores = torch.empty(batch, q_heads, num_blocks, dtype=torch.float32, device=device)
+    if tuple(scores.shape) != (batch, q_heads, num_blocks) or scores.dtype != torch.float32 or not scores.is_contiguous():
+        raise ValueError("scores must be a contiguous float32 [batch, q_heads, blocks] tensor")
+    lens_dtype = SA_INDEX[seq_lens.dtype] if seq_lens is not None else 0
+    with torch.cuda.device(device):
+        rc = load().sa_block_scores(_ptr(query), _ptr(key), _ptr(scores), _ptr(seq_lens), lens_dtype, batch, q_heads,
+                                    kv_heads, dim, kv_len, q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+                                    int(block_size), SA_SELECTOR[selector], stream_handle(device))
+    check(rc)
+    return scores
+
+
+def seed_list_length(kv_len: int, block_size: int, sink_blocks: int, recent_blocks: int,
+                     middle_seed_blocks: int) -> int:
+    n = int(load().sa_seed_list_length(int(kv_len), int(block_size), int(sink_blocks), int(recent_blocks),
+                                       int(middle_seed_blocks)))
+    if n < 0:
+        raise ValueError(last_error())
+    return n
+
+
+def select_seed_blocks(scores: torch.Tensor, *, kv_heads: int, kv_len: int, block_size: int, sink_blocks: int,
+                       recent_blocks: int, middle_seed_blocks: int, block_order: str,
+                       blocks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per (row, KV head) block lists ``[B, Hkv, L]`` (int32, ascending) from block scores."""
+
+    device = require_cuda(scores, blocks)
+    if block_order not in SA_BLOCK_ORDER:
+        raise ValueError("block_order must be sequential, recent_first, or sink_recent_first")
+    if scores.dtype != torch.float32 or scores.dim() != 3 or not scores.is_contiguous():
+        raise ValueError("scores must be a contiguous float32 [batch, q_heads, blocks] tensor")
+    batch, q_heads, num_blocks = map(int, scores.shape)
+    if num_blocks != -(-int(kv_len) // int(block_size)):
+        raise ValueError("scores do not cover ceil(kv_len / block_size) blocks")
+    length = seed_list_length(kv_len, block_size, sink_blocks, recent_blocks, middle_seed_blocks)
+    if blocks is None:
+        blocks = torch.empty(batch, int(kv_heads), length, dtype=torch.int32, device=device)
+    if tuple(blocks.shape) != (batch, int(kv_heads), length) or blocks.dtype != torch.int32 or not blocks.is_contiguous():
+        raise ValueError("blocks must be a contiguous int32 [batch, kv_heads, list length] tensor")
+    with torch.cuda.device(device):
+        rc = load().sa_select_seed_blocks(_ptr(scores), _ptr(blocks), batch, q_heads, int(kv_heads), int(kv_len),
+                                          int(block_size), int(sink_blocks), int(recent_blocks),
+                                          int(middle_seed_blocks), SA_BLOCK_ORDER[block_order], stream_handle(device))
+    check(rc)
+    return blocks
+
+
+def seed_plan_device_blocks(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
+                            workspace: torch.Tensor, blocks: torch.Tensor, *, block_size: int,
+                            includes_last_block: bool = True, kv_layout: str = "BNHD", num_ctas: int = 0,
+                            kernel: str = "auto") -> NativePlan:
+    """Seed-only plan whose per-pair block lists ``[B, Hkv, L]`` (int32) are read on the device at run time."""
+
+    device = require_cuda(key, value, workspace, blocks, host_io=(query, output))
+    if query.dtype not in SA_DTYPE or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query/key/value must share a dtype of bf16, fp16 or fp32")
+    q_sb, q_sh = _q_strides(query)
+    kv_heads, kv_len, sb, sn, sh = _kv_geometry(key, value, kv_layout)
+    batch, _, q_heads, dim = map(int, query.shape)
+    if int(key.shape[0]) != batch or int(key.shape[3]) != dim:
+        raise ValueError("query/KV batch and head_dim must match")
+    _check_output(output, query, False)
+    if blocks.dtype != torch.int32 or blocks.dim() != 3 or tuple(blocks.shape[:2]) != (batch, kv_heads) \
+            or not blocks.is_contiguous():
+        raise ValueError("blocks must be a contiguous int32 [batch, kv_heads, list length] tensor")
+    with torch.cuda.device(device):
+        handle = load().sa_seed_plan_create_device(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(workspace), workspace.numel(),
+            batch, q_heads, kv_heads, dim, kv_len, q_sb, q_sh, sb, sn, sh, SA_DTYPE[query.dtype],
+            int(block_size), _ptr(blocks), int(blocks.shape[2]), int(bool(includes_last_block)), int(num_ctas),
+            SA_KERNEL[kernel],
+        )
+    return NativePlan(handle, device, (query, key, value, output, workspace, blocks))
 
 
 def merge_states(states: torch.Tensor, output: torch.Tensor) -> torch.Tensor:

@@ -153,6 +153,28 @@ SEED_CASES: Dict[str, SeedCase] = {
     ]
 }
 
+# Run-time seed selection (one KV head per query head, so the reference's per-head selection and
+# the per-(row, KV head) selection of the kernels coincide): reuses SeedCase with q_heads == kv_heads.
+SELECT_CASES: Dict[str, SeedCase] = {
+    c.name: c
+    for c in [
+        SeedCase("sel_bs32_d128", 40, 2, 3, 3, 128, 1000, 32, 2, 2, 8, "recent_first"),
+        SeedCase("sel_bs16_d64", 41, 1, 4, 4, 64, 777, 16, 1, 3, 4, "sequential"),
+        SeedCase("sel_bs8_d64_short", 42, 2, 2, 2, 64, 50, 8, 1, 1, 3, "recent_first"),
+    ]
+}
+SELECTORS = ("qk_block_max", "block_mean_proxy")
+
+
+def select_inputs(case: SeedCase):
+    """q, k rounded to bf16 (returned as float32) so CPU reference and GPU kernels see the same values."""
+
+    g = _gen(case.seed)
+    q = torch.randn(case.batch, 1, case.q_heads, case.dim, generator=g).bfloat16().float()
+    k = torch.randn(case.batch, case.kv_len, case.kv_heads, case.dim, generator=g).bfloat16().float()
+    return q, k
+
+
 # Parameter grid for the integer seed-set goldens:
 # (seq_len, block_size, sink, recent, middle, order)
 SEED_INDEX_GRID: List[Tuple[int, int, int, int, int, str]] = [

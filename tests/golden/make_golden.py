@@ -347,6 +347,39 @@ def route_policy_goldens(ref) -> None:
     (HERE / "route_policy.json").write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n")
 
 
+def seed_selection_goldens(ref) -> None:
+    """Run-time seed selection as the reference computes it (seed_selectors.py:274-396): block
+    scores of `_score_tensor_for_runtime_selector` and the blocks `select_seed_blocks_by_profile`
+    picks, per (row, head), for the selectors that need only q and K."""
+
+    from types import SimpleNamespace
+
+    from stream_attention import seed_selectors as ref_sel
+
+    out = {}
+    for name, case in cases.SELECT_CASES.items():
+        q, k = cases.select_inputs(case)
+        policy = SimpleNamespace(block_size=case.block_size, sink_blocks=case.sink_blocks,
+                                 recent_blocks=case.recent_blocks, middle_seed_blocks=case.middle_seed_blocks,
+                                 block_order=case.block_order)
+        entry = {}
+        for selector in cases.SELECTORS:
+            scores, selected = [], []
+            for b in range(case.batch):
+                scores.append([])
+                selected.append([])
+                for h in range(case.q_heads):
+                    s = ref_sel._score_tensor_for_runtime_selector(q[b, 0, h], k[b, :, h], block_size=case.block_size,
+                                                                   selector=selector)
+                    pick = ref_sel.select_seed_blocks_by_profile(q=q[b, 0, h], k=k[b, :, h], policy=policy,
+                                                                 selector=selector)
+                    scores[b].append([float(x) for x in s.tolist()])
+                    selected[b].append(sorted(int(x) for x in pick.selected_blocks))
+            entry[selector] = {"scores": scores, "selected": selected}
+        out[name] = entry
+    (HERE / "seed_selection.json").write_text(json.dumps(out, indent=None, sort_keys=True) + "\n")
+
+
 def rope_append_goldens(ref_root: Path) -> None:
     """RoPE + append through the reference's own safe path (`_apply_qwen_rope` + `copy_`,
     benchmarks/profile_seed_only_fused_rope_parity.py:24-30, 97-102), on CPU tensors."""
@@ -391,6 +424,7 @@ def main() -> None:
     seed_goldens(ref, ref_root)
     host_contract_goldens(ref)
     route_policy_goldens(ref)
+    seed_selection_goldens(ref)
     rope_append_goldens(ref_root)
     print("fixtures written to", HERE)
 

@@ -30,6 +30,14 @@ def _close(got, want, atol=2e-2, mean=2e-3):
     assert float(diff.max()) <= atol and float(diff.mean()) <= mean, (float(diff.max()), float(diff.mean()))
 
 
+def _one_rounding(got, want, dtype=torch.bfloat16, slack=1e-3):
+    """|got - want| within one rounding of the output dtype (projection outputs are not O(1))."""
+
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    diff = (got.float().cpu() - want.float()).abs()
+    assert bool((diff <= want.float().abs() * ulp + slack).all()), float(diff.max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("batch,in_features,out_features,has_bias", [
     (5, 64, 96, False), (5, 64, 96, True),          # the reference test's shape
@@ -46,9 +54,7 @@ def test_o_proj_matches_float32_linear(dev, dtype, batch, in_features, out_featu
     got = sa.qwen_o_proj_forward(x.to(dev), weight.to(dev), None if bias is None else bias.to(dev))
     assert got.shape == (batch, 1, out_features) and got.dtype == dtype
     torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=1e-2)          # the reference's bar
-    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
-    bound = want.abs() * ulp + 1e-3
-    assert bool(((got.float().cpu() - want).abs() <= bound).all()), "more than one output rounding away"
+    _one_rounding(got, want, dtype)
 
 
 def test_o_proj_plan_reads_a_strided_attention_buffer_and_allocates_nothing(dev):
@@ -65,11 +71,11 @@ def test_o_proj_plan_reads_a_strided_attention_buffer_and_allocates_nothing(dev)
         assert plan.run() is out
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated(dev) == before
-    _close(out, want, atol=3e-2, mean=4e-3)
+    _one_rounding(out, want)
     # in-place update of the bound input is seen by the next run
     attn.mul_(-1)
     plan.run()
-    _close(out, -want, atol=3e-2, mean=4e-3)
+    _one_rounding(out, -want)
     # without the early weight fetch the result is the same bits
     late = sa.OProjPlan.build(attn.view(batch, 1, heads * dim), weight, prefetch_weights=False)
     assert torch.equal(late.run(), out)
@@ -105,7 +111,9 @@ def test_decode_then_projection_chain_matches_the_oracle(dev):
     for _ in range(3):
         plan.run()
         out = proj.run()
-    _close(out, want, atol=3e-2, mean=4e-3)
+    # the attention output itself is within 2e-2 of the oracle's; through a 1/16-scaled weight of
+    # `hidden` columns that is at most a few hundredths on outputs of magnitude ~1
+    _close(out, want, atol=6e-2, mean=1e-2)
 
 
 def test_reference_named_launchers(dev):
