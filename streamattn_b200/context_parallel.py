@@ -167,6 +167,14 @@ class ContextParallelExactDecode:
         if self.exchange == "nccl":
             self.gathered = torch.empty(self.world_size, batch, q_heads, dim + 2, dtype=torch.float32,
                                         device=device)
+        # The exchange kernels wait for their peers for at most the wait limit (2 s by default).
+        # Run the shard kernel once here - it loads the kernel image, the slow part of a first
+        # launch - and line the ranks up, so that the first exchanged step starts everywhere at
+        # about the same time.  Results of run() are valid only while device_status() stays 0.
+        self._plan.run()
+        torch.cuda.synchronize(device)
+        if self.world_size > 1:
+            dist.barrier(group)
 
     @property
     def kernel_name(self) -> str:
