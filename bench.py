@@ -70,8 +70,8 @@ NCU_TRAFFIC = {
     "exact_c2": (272.3e6, "profiles/stream_decode_exact_c2.md"),
     "paged_c3": (170.9e6, "profiles/stream_decode_paged_c3.md"),
     # one eighth of the 1M-token row was captured; traffic grows in proportion to the tokens read
-    "cp_c5": (8 * 541.7e6, "profiles/stream_decode_cp_shard_d128.md"),
-    "cp_c5_1gpu": (8 * 541.7e6, "profiles/stream_decode_cp_shard_d128.md"),
+    "cp_c5": (8 * 540.5e6, "profiles/stream_decode_cp_shard_d128.md"),
+    "cp_c5_1gpu": (8 * 540.5e6, "profiles/stream_decode_cp_shard_d128.md"),
 }
 
 

@@ -71,45 +71,26 @@ class SeedKernelShape:
             if getattr(self, name) < 0:
                 raise ValueError(f"{name} must be non-negative")
 
-    @property
-    def group_size(self) -> int:
-        return self.q_heads // self.kv_heads
+    # Derived quantities (names and values as in the reference's record, whose to_dict() is the
+    # interchange format).  Byte counts are K plus V over `heads` heads and `tokens` tokens.
 
-    @property
-    def seed_blocks(self) -> int:
-        return self.sink_blocks + self.recent_blocks + self.middle_seed_blocks
+    def _kv_bytes(self, heads: int, tokens: int) -> int:
+        return 2 * self.batch * heads * tokens * self.dim * self.dtype_bytes
 
-    @property
-    def seed_tokens(self) -> int:
-        return min(self.kv_len, self.seed_blocks * self.block_size)
-
-    @property
-    def seed_token_ratio(self) -> float:
-        return float(self.seed_tokens) / float(self.kv_len)
-
-    @property
-    def head_private_kv_byte_ratio(self) -> float:
-        """Seed K/V bytes over exact K/V bytes if every query head reloaded the seed K/V."""
-
-        return float(self.group_size) * self.seed_token_ratio
-
-    @property
-    def gqa_shared_kv_byte_ratio(self) -> float:
-        """Seed K/V bytes over exact K/V bytes with K/V shared inside a group (what the kernel does)."""
-
-        return self.seed_token_ratio
-
-    @property
-    def exact_kv_bytes(self) -> int:
-        return 2 * self.batch * self.kv_heads * self.kv_len * self.dim * self.dtype_bytes
-
-    @property
-    def head_private_seed_kv_bytes(self) -> int:
-        return 2 * self.batch * self.q_heads * self.seed_tokens * self.dim * self.dtype_bytes
-
-    @property
-    def gqa_shared_seed_kv_bytes(self) -> int:
-        return 2 * self.batch * self.kv_heads * self.seed_tokens * self.dim * self.dtype_bytes
+    group_size = property(lambda self: self.q_heads // self.kv_heads, doc="query heads per KV head")
+    seed_blocks = property(lambda self: self.sink_blocks + self.recent_blocks + self.middle_seed_blocks)
+    seed_tokens = property(lambda self: min(self.kv_len, self.seed_blocks * self.block_size),
+                           doc="tokens the seed schedule reads (the cache length at most)")
+    seed_token_ratio = property(lambda self: self.seed_tokens / float(self.kv_len))
+    head_private_kv_byte_ratio = property(
+        lambda self: self.group_size * self.seed_token_ratio,
+        doc="seed K/V bytes over exact K/V bytes if every query head reloaded the seed K/V")
+    gqa_shared_kv_byte_ratio = property(
+        lambda self: self.seed_token_ratio,
+        doc="seed K/V bytes over exact K/V bytes with K/V shared inside a group (what the kernel does)")
+    exact_kv_bytes = property(lambda self: self._kv_bytes(self.kv_heads, self.kv_len))
+    head_private_seed_kv_bytes = property(lambda self: self._kv_bytes(self.q_heads, self.seed_tokens))
+    gqa_shared_seed_kv_bytes = property(lambda self: self._kv_bytes(self.kv_heads, self.seed_tokens))
 
     # -- what the streaming kernel makes of the shape ---------------------------------------
 
