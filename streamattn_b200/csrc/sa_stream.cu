@@ -65,10 +65,11 @@ struct StreamParams {
 
 // Instrumented builds (-DSA_TIMELINE) record %globaltimer per CTA at a few points of the kernel.
 #ifdef SA_TIMELINE
-#define SA_STAMP(i) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = global_timer_ns(); } while (0)
+#define SA_STAMP_VALUE(i, v) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = (v); } while (0)
 #else
-#define SA_STAMP(i) do { } while (0)
+#define SA_STAMP_VALUE(i, v) do { } while (0)
 #endif
+#define SA_STAMP(i) SA_STAMP_VALUE(i, global_timer_ns())
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -96,6 +97,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "r"(bar), "r"(parity)
         : "memory");
     return ok;
+}
+
+__device__ __forceinline__ unsigned sm_id()
+{
+    unsigned id;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(id));
+    return id;
 }
 
 __device__ __forceinline__ unsigned long long global_timer_ns()
@@ -561,6 +569,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     uint8_t *warp_ring = ring + warp * STAGES * kStageBytes;
 
     SA_STAMP(0);
+    SA_STAMP_VALUE(2, sm_id());  // which SM ran this CTA
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_v)) : "memory");
