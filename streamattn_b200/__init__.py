@@ -69,7 +69,15 @@ from .bucket_policy import (
 )
 from .o_proj import OProjPlan, qwen_o_proj_forward
 from .kv_update import AppendKVPlan, PagedKVWriter, PagePool, append_kv, paged_append_kv
-from .seed_selectors import policy_seed_blocks, seed_indices, seed_token_indices_from_blocks
+from .seed_selectors import (
+    DynamicSeedDecodePlan,
+    SeedBlockSelection,
+    parse_selector_profiles,
+    policy_seed_blocks,
+    seed_indices,
+    seed_token_indices_from_blocks,
+    select_seed_blocks_by_profile,
+)
 
 # ``import streamattn_b200 as stream_attn; stream_attn.decode(...)``
 decode = stream_attn_decode

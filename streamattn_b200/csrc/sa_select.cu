@@ -45,7 +45,7 @@ template <typename T>
 __global__ void __launch_bounds__(kScoreWarps * 32)
 block_scores_kernel(const __grid_constant__ ScoreParams p)
 {
-    extern __shared__ float q_sm[];  // [group][head_dim]
+    extern __shared__ __align__(16) float q_sm[];  // [group][head_dim]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int group = p.q_heads / p.kv_heads;
@@ -134,7 +134,7 @@ __device__ __forceinline__ bool is_base_block(const SelectParams &p, int blk)
 __global__ void __launch_bounds__(kSelectThreads)
 select_blocks_kernel(const __grid_constant__ SelectParams p)
 {
-    extern __shared__ float pair_scores[];  // [num_blocks]: max over the group's heads, -inf once taken/base
+    extern __shared__ __align__(16) float pair_scores[];  // [num_blocks]: max over the group's heads, -inf once taken/base
     __shared__ float red_score[kSelectThreads / 32];
     __shared__ int red_index[kSelectThreads / 32];
     __shared__ int chosen[SA_MAX_SEED_BLOCKS];

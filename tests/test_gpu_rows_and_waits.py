@@ -188,3 +188,43 @@ def test_wait_limit_arguments_are_checked(dev):
     assert lib.sa_set_wait_limit_ns(ctypes.c_uint64(0)) == native.SA_ERR_INVALID
     assert lib.sa_plan_set_wait_limit_ns(None, ctypes.c_uint64(5)) == native.SA_ERR_INVALID
     assert lib.sa_plan_set_rows(None, None, 0, 0) == native.SA_ERR_INVALID
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_exchange_data_path_of_many_ranks_on_one_gpu(dev, world):
+    """The 4- and 8-rank exchange (addresses, strides, merge over all ranks) checked on ONE GPU
+    without two kernels ever waiting on each other: the ranks' launches run one after the other,
+    each with a 0.3 ms wait limit.  All but the last give up their wait (and say so); the last
+    one finds every rank's words of the step already in its buffer and must produce the exact
+    result.  The launch order rotates, so different ranks come last in different steps."""
+
+    case = cases.EXACT_CASES["g4_d128_n257"]
+    q, k, v = (t.bfloat16() for t in cases.exact_inputs(case))
+    want = cpu_oracle.exact_decode(q, k, v)
+    batch, q_heads, kv_heads, dim = case.batch, case.q_heads, case.kv_heads, case.dim
+    qd = q.to(dev)
+    nbytes = native.cp_fused_bytes(world, batch, q_heads, kv_heads, dim)
+    buffers = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in buffers]
+    plans, outs, spaces = [], [], []
+    for r in range(world):
+        lo, hi = case.kv_len * r // world, case.kv_len * (r + 1) // world
+        kh = k[:, lo:hi].permute(0, 2, 1, 3).contiguous().to(dev)
+        vh = v[:, lo:hi].permute(0, 2, 1, 3).contiguous().to(dev)
+        out = torch.zeros_like(qd)
+        ws = native.new_workspace(dev, batch, q_heads, kv_heads, dim)
+        plan = native.cp_fused_plan(qd, kh, vh, out, ws, ptrs, r)
+        plan.set_wait_limit_ns(300_000)
+        plans.append(plan)
+        outs.append(out)
+        spaces.append(ws)
+    for step in range(3):
+        order = [(step * 3 + i) % world for i in range(world)]
+        for r in order:
+            plans[r].run()
+            torch.cuda.synchronize()
+        last = order[-1]
+        _close(outs[last], want)
+        for r in order:
+            status = native.workspace_status(spaces[r])
+            assert (status == 0) == (r == last), (step, r, status)
