@@ -385,24 +385,25 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsig
 // last CTA to arrive on it (items <= NTHREADS).  A work item is 4 columns of one head row;
 // NTHREADS / items threads share an item and each takes every (NTHREADS / items)-th state,
 // requesting its o rows together with their (m, l) in one batch, so the whole merge costs one
-// round trip to L2.  The CTA's own state (index `self`) does not make that trip: it is taken
-// from shared memory (`own`: o[4], m, l per item) and enters the sum at its index position, so
-// the order of the additions - and with it every bit of the result - does not depend on which
-// CTA happens to arrive last.
+// round trip to L2 (loads with gpu-scope semantics are costly to issue: BATCH, the states one
+// thread requests per pass, is chosen to fit the pair).  The CTA's own state (index `self`) does
+// not make that trip: it is taken from shared memory (`own`: o[4], m, l per item) and enters the
+// sum at its index position, so the order of the additions - and with it every bit of the result
+// - does not depend on which CTA happens to arrive last.
 // The other states are published with inverted bits (see state_load4): a word that still reads
 // zero has not landed yet and the batch is requested again, for at most `wait_ns`.  Every other
 // CTA of the pair took its ticket earlier, i.e. has left its streaming loop and is combining and
 // storing its state: the wait is for a few hundred nanoseconds of work of CTAs that are already
 // running, never for a CTA that still has to be scheduled.  The per-thread results meet in shared
 // memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l) and all nseg states are zero
-// again.  Out of line so that the rows in flight do not weigh on the streaming loop's registers.
-template <int D, int NTHREADS>
-__device__ __noinline__ void merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
-                                               const float *own, int items, float *sm, int tid,
-                                               unsigned long long wait_ns, int *status)
+// again.  Returns how often this thread had to ask again.  Out of line so that the rows in
+// flight do not weigh on the streaming loop's registers.
+template <int D, int NTHREADS, int BATCH>
+__device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
+                                              const float *own, int items, float *sm, int tid,
+                                              unsigned long long wait_ns, int *status)
 {
     constexpr int PART_STRIDE = D + 4;
-    constexpr int BATCH = 10;  // states per thread and pass: 20 split states in one pass at two threads per item
     const int parts = NTHREADS / items;
     const int part = tid / items;
     const int item = tid - part * items;
@@ -510,6 +511,7 @@ __device__ __noinline__ void merge_pair_states(float *first_slot, int64_t slot_s
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
     __syncthreads();
+    return static_cast<int>(polls);
 }
 
 // One fragment (TMA box) of a tile as seen by the issuing lane.
@@ -1003,7 +1005,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 seq_i = n_w;
                 break;
             }
-            if (j == 0) SA_STAMP(7);
 
             const int64_t tile_tok0 = static_cast<int64_t>(lt) * TILE_N;
             const int n_valid = vlen - tile_tok0 < TILE_N ? static_cast<int>(vlen - tile_tok0) : TILE_N;
@@ -1206,7 +1207,8 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         // The pair's ticket is taken now, before this CTA's state is even combined: it counts the
         // CTAs that have finished streaming and elects the last of them as the merger.  The
         // merger recognises a state that has landed by its contents, so the ticket orders
-        // nothing, and its round trip overlaps the combine below.
+        // nothing, and its round trip overlaps the combine below.  (Asking for it earlier still,
+        // when the last tile of warp 0 lands, measured slower on every workload.)
         int old_count = 0;
         if (nseg > 1 && tid == 0)
             asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], 1;"
@@ -1282,9 +1284,27 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     if (r0 >= group) continue;
                     const int n_rows = group - r0 < MERGE_ROWS ? group - r0 : MERGE_ROWS;
                     const int sub_items = n_rows * (D / 4);
-                    merge_pair_states<D, NTHREADS>(first_slot + r0 * PART_STRIDE, slot_stride, nseg, c - first_cta,
-                                                   states + k * NTHREADS * 6, sub_items, scratch, tid, p.wait_ns,
-                                                   p.status);
+                    // States each thread has to fetch: the batch size that covers them in one pass.
+                    const int per_thread = (nseg + NTHREADS / sub_items - 1) / (NTHREADS / sub_items);
+                    float *slots = first_slot + r0 * PART_STRIDE;
+                    const float *mine = states + k * NTHREADS * 6;
+                    int polls;
+                    if (per_thread <= 3)
+                        polls = merge_pair_states<D, NTHREADS, 3>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
+                    else if (per_thread <= 6)
+                        polls = merge_pair_states<D, NTHREADS, 6>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
+                    else
+                        polls = merge_pair_states<D, NTHREADS, 10>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                   sub_items, scratch, tid, p.wait_ns, p.status);
+#ifdef SA_TIMELINE
+                    {
+                        const int most = __reduce_max_sync(0xffffffffu, polls);  // of warp 0
+                        SA_STAMP_VALUE(7, 1000 + most);
+                    }
+#endif
+                    (void)polls;
                     if (tid < sub_items) {
                         const int row = tid / (D / 4);
                         const float *r = scratch + tid * 6;
