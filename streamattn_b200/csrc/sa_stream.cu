@@ -59,17 +59,27 @@ struct StreamParams {
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
-    unsigned long long *timeline;  // instrumented builds only: 8 globaltimer stamps per CTA
+    unsigned long long *timeline;  // instrumented builds only: 16 words (globaltimer stamps, SM, poll count) per CTA
 #endif
 };
 
 // Instrumented builds (-DSA_TIMELINE) record %globaltimer per CTA at a few points of the kernel.
 #ifdef SA_TIMELINE
-#define SA_STAMP_VALUE(i, v) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 8 + (i)] = (v); } while (0)
+#define SA_STAMP_VALUE(i, v) do { if (p.timeline != nullptr && tid == 0) p.timeline[blockIdx.x * 16 + (i)] = (v); } while (0)
 #else
 #define SA_STAMP_VALUE(i, v) do { } while (0)
 #endif
 #define SA_STAMP(i) SA_STAMP_VALUE(i, global_timer_ns())
+// The merge is out of line: instrumented builds hand it the CTA's row of the stamp buffer.
+#ifdef SA_TIMELINE
+#define SA_TL_PARAM , unsigned long long *tl_row
+#define SA_TL_ARG , (p.timeline != nullptr ? p.timeline + blockIdx.x * 16 : nullptr)
+#define SA_TL_STAMP(i) do { if (tl_row != nullptr && tid == 0) tl_row[i] = global_timer_ns(); } while (0)
+#else
+#define SA_TL_PARAM
+#define SA_TL_ARG
+#define SA_TL_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -401,9 +411,10 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsig
 template <int D, int NTHREADS, int BATCH>
 __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
                                               const float *own, int items, float *sm, int tid,
-                                              unsigned long long wait_ns, int *status)
+                                              unsigned long long wait_ns, int *status SA_TL_PARAM)
 {
     constexpr int PART_STRIDE = D + 4;
+    SA_TL_STAMP(10);
     const int parts = NTHREADS / items;
     const int part = tid / items;
     const int item = tid - part * items;
@@ -448,6 +459,7 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
                 }
             }
         }
+        SA_TL_STAMP(11);
         {   // the CTA's own state takes its place in the sequence (stored like the others)
             const float *mine = own + item * 6;
 #pragma unroll
@@ -486,6 +498,7 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
     __syncthreads();  // every thread has read its states: they can be cleared
+    SA_TL_STAMP(12);
     if (active) {
         for (int i = part; i < nseg; i += parts) {
             state_store4(src + i * slot_stride + d4, 0u, 0u, 0u, 0u);
@@ -511,6 +524,7 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
     __syncthreads();
+    SA_TL_STAMP(13);
     return static_cast<int>(polls);
 }
 
@@ -587,6 +601,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // order is unchanged; only launch latency and the set-up above overlap the previous tail.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    SA_STAMP(14);
     if (ragged) {
         // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
         const bool subset = p.seq.num_rows >= 0;
@@ -631,6 +646,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     }
     fence_proxy_async();
 
+    SA_STAMP(8);
     const uint64_t policy = make_evict_first_policy();
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
     // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
@@ -901,6 +917,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
     };
 
+    SA_STAMP(9);
     // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
     Frag first[STAGES + 1];
 #pragma unroll
@@ -1291,13 +1308,13 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     int polls;
                     if (per_thread <= 3)
                         polls = merge_pair_states<D, NTHREADS, 3>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
                     else if (per_thread <= 6)
                         polls = merge_pair_states<D, NTHREADS, 6>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
                     else
                         polls = merge_pair_states<D, NTHREADS, 10>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                   sub_items, scratch, tid, p.wait_ns, p.status);
+                                                                   sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
 #ifdef SA_TIMELINE
                     {
                         const int most = __reduce_max_sync(0xffffffffu, polls);  // of warp 0
@@ -1386,7 +1403,7 @@ cudaError_t launch_dim(const CUtensorMap &mk, const CUtensorMap &mv, const Strea
 }  // namespace
 
 #ifdef SA_TIMELINE
-// Instrumented builds only: where the kernels write their per-CTA time stamps (8 per CTA).
+// Instrumented builds only: where the kernels write their per-CTA time stamps (16 words per CTA).
 unsigned long long *g_timeline = nullptr;
 extern "C" __attribute__((visibility("default"))) void sa_debug_timeline(void *ptr)
 {
