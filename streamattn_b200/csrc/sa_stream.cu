@@ -415,8 +415,11 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
 {
     constexpr int PART_STRIDE = D + 4;
     SA_TL_STAMP(10);
-    const int parts = NTHREADS / items;
-    const int part = tid / items;
+    // Small non-negative integers: floor(a / b) = floor((a + 0.5) * (1 / b)) without the long
+    // integer-division sequence (the half keeps the product clear of the next integer).
+    const float inv_items = __frcp_rn(static_cast<float>(items));
+    const int parts = static_cast<int>((static_cast<float>(NTHREADS) + 0.5f) * inv_items);
+    const int part = static_cast<int>((static_cast<float>(tid) + 0.5f) * inv_items);
     const int item = tid - part * items;
     const bool active = part < parts;
     const int row = item / (D / 4);
@@ -501,8 +504,9 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
     SA_TL_STAMP(12);
     if (active) {
         for (int i = part; i < nseg; i += parts) {
-            state_store4(src + i * slot_stride + d4, 0u, 0u, 0u, 0u);
-            if (d4 == 0) state_store2(src + i * slot_stride + D, 0u, 0u);
+            // Plain stores: the next reader is a later launch, which the launch boundary orders.
+            *reinterpret_cast<float4 *>(src + i * slot_stride + d4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (d4 == 0) *reinterpret_cast<float2 *>(src + i * slot_stride + D) = make_float2(0.0f, 0.0f);
         }
     }
     if (part == 0 && parts > 1) {
@@ -1224,8 +1228,9 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         // The pair's ticket is taken now, before this CTA's state is even combined: it counts the
         // CTAs that have finished streaming and elects the last of them as the merger.  The
         // merger recognises a state that has landed by its contents, so the ticket orders
-        // nothing, and its round trip overlaps the combine below.  (Asking for it earlier still,
-        // when the last tile of warp 0 lands, measured slower on every workload.)
+        // nothing, and its round trip overlaps the combine below.  (Asking for it earlier still -
+        // when the last tile of warp 0 lands, or right after the tile loop - measured slower: the
+        // merger then looks before the last states have landed and pays a second round trip.)
         int old_count = 0;
         if (nseg > 1 && tid == 0)
             asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], 1;"
@@ -1302,7 +1307,10 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     const int n_rows = group - r0 < MERGE_ROWS ? group - r0 : MERGE_ROWS;
                     const int sub_items = n_rows * (D / 4);
                     // States each thread has to fetch: the batch size that covers them in one pass.
-                    const int per_thread = (nseg + NTHREADS / sub_items - 1) / (NTHREADS / sub_items);
+                    const int sharers = static_cast<int>(
+                        (static_cast<float>(MERGE_ROWS) + 0.5f) * __frcp_rn(static_cast<float>(n_rows)));  // threads per item
+                    const int per_thread = static_cast<int>(
+                        (static_cast<float>(nseg + sharers - 1) + 0.5f) * __frcp_rn(static_cast<float>(sharers)));
                     float *slots = first_slot + r0 * PART_STRIDE;
                     const float *mine = states + k * NTHREADS * 6;
                     int polls;
