@@ -12,19 +12,25 @@ once per KV head and shares it among the query heads of the group, so the only
 thing left to choose is how many CTAs work on one (row, KV head) pair.  A
 candidate is therefore "``seed_chunks`` CTAs per pair"; its cost comes from a
 latency model of the kernel fitted to a sweep on a B200 (batch 1-8, 128-1024 seed
-tokens, 1-16 CTAs per pair; the model's choice is within 3 % of the best measured
-grid on every cell of that sweep):
+tokens, 1-16 CTAs per pair; the model picks the fastest measured grid on every
+cell of that sweep):
 
-``t = T0 + rounds * T_ROUND + tiles_per_cta * T_TILE + merge(chunks)``
+``t = T0 + rounds * T_ROUND + tiles_per_cta * T_TILE + partition(chunks) + merge(chunks)``
 
 * a CTA has 8 warps with one 16 KB K+V tile in flight each, so it needs
   ``rounds = ceil(tiles_per_cta / 8)`` trips to HBM (``T_ROUND`` each) and moves
   its tiles at about 110 GB/s per SM (``T_TILE`` per tile);
-* more than one CTA per pair adds the in-launch merge of their split states:
-  a ticket, one round trip to L2 per batch of states, the output store.
+* from four CTAs per pair on, the kernel snaps the CTAs' slices to pair boundaries,
+  which costs half a microsecond at the head of the launch; with two or three it
+  cuts the tile list into equal slices, and unless a pair's tiles divide evenly one
+  CTA then straddles two pairs and flushes its state twice (``STRADDLE_US``);
+* more than one CTA per pair adds the in-launch merge of their split states: a
+  ticket, one round trip to L2 for the states (the merging CTA asks for 3, 6 or 10
+  states per thread, whichever covers the pair; more states take further round
+  trips), the output store.
 
 Few seed tokens are served fastest by ONE CTA per pair (no merge at all); from
-about 20 tiles per pair on, splitting the pair over several CTAs wins.
+about 12 tiles per pair on, splitting the pair over several CTAs wins.
 """
 
 from __future__ import annotations
@@ -38,12 +44,14 @@ TILE_BYTES = 16384          # one K tile + one V tile of the streaming kernel
 WARPS_PER_CTA = 8
 # Fitted constants, microseconds (B200, SM clock 1965 MHz, programmatic dependent launch on).
 T0_US = 3.5                 # launch, set-up, first request leaves the SM, output store
-T_ROUND_US = 0.8            # one more dependent trip to HBM for a warp
+T_ROUND_US = 0.9            # one more dependent trip to HBM for a warp
 T_TILE_US = 0.15            # 16 KB through one SM
-MERGE_SMALL_US = 2.4        # 2-3 CTAs per pair
-MERGE_US = 3.3              # 4 and more
-MERGE_EXTRA_PASS_US = 1.7   # per further batch of split states the merging CTA has to request
-MERGE_STATES_PER_THREAD = 10
+ALIGNED_CHUNKS = 4          # CTAs per pair from which the slices are snapped to pair boundaries
+ALIGNED_US = 0.5            # ... and what working that partition out costs
+STRADDLE_US = 3.5           # equal slices that do not end on pair boundaries: a CTA flushes twice
+MERGE_TIERS_US = ((3, 1.8), (6, 2.35), (10, 3.0))  # (states per thread the batch covers, cost)
+MERGE_EXTRA_PASS_US = 1.9   # per further batch of split states the merging CTA has to request
+MERGE_STATES_PER_THREAD = MERGE_TIERS_US[-1][0]
 
 
 @dataclass(frozen=True)
@@ -186,12 +194,18 @@ def predicted_seed_decode_us(shape: SeedKernelShape, chunks: int) -> float:
     rounds = math.ceil(tiles_per_cta / WARPS_PER_CTA)
     t = T0_US + rounds * T_ROUND_US + tiles_per_cta * T_TILE_US
     if chunks > 1:
-        # The merging CTA requests MERGE_STATES_PER_THREAD states per thread and pass; 256 threads
-        # share the (head row, 4 columns) work items of the group.
+        if chunks >= ALIGNED_CHUNKS:
+            t += ALIGNED_US
+        elif shape.tiles_per_pair % chunks:
+            t += STRADDLE_US
+        # 256 threads share the (head row, 4 columns) work items of the group; each requests the
+        # states of its item in batches sized to the pair.
         items = shape.group_size * max(1, shape.dim // 4)
         threads_per_item = max(1, (WARPS_PER_CTA * 32) // items)
-        passes = math.ceil(chunks / (MERGE_STATES_PER_THREAD * threads_per_item))
-        t += (MERGE_SMALL_US if chunks <= 3 else MERGE_US) + (passes - 1) * MERGE_EXTRA_PASS_US
+        per_thread = math.ceil(chunks / threads_per_item)
+        passes = math.ceil(per_thread / MERGE_STATES_PER_THREAD)
+        t += next((cost for covers, cost in MERGE_TIERS_US if per_thread <= covers), MERGE_TIERS_US[-1][1])
+        t += (passes - 1) * MERGE_EXTRA_PASS_US
     return t
 
 
