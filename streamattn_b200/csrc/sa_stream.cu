@@ -600,11 +600,14 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Programmatic dependent launch: let the next kernel of the stream be scheduled as this
-    // grid's CTAs retire, and hold this grid here - before its first global-memory access -
-    // until everything launched earlier in the stream has completed and is visible.  Stream
-    // order is unchanged; only launch latency and the set-up above overlap the previous tail.
+    // grid's CTAs retire, and hold this grid - before its first global-memory access - until
+    // everything launched earlier in the stream has completed and is visible.  Stream order is
+    // unchanged; only launch latency and whatever runs before the wait overlap the previous
+    // tail.  Rows of one length need nothing from memory to cut the tile list, so for them the
+    // wait comes after the partition (below, in front of the first table look-ups and copies);
+    // ragged rows read their lengths first and wait here.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (ragged) asm volatile("griddepcontrol.wait;" ::: "memory");
     SA_STAMP(14);
     if (ragged) {
         // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
@@ -921,11 +924,17 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
     };
 
+    // Rows of one length: the dependency wait (see the note at launch_dependents) comes here, or
+    // - when working out the first tiles' coordinates reads no memory either (no device-resident
+    // block lists, no claim counter) - after that as well.
+    const bool lookups_first = !ragged && p.seq.blocks_dev == nullptr && !dyn_claims;
+    if (!ragged && !lookups_first) asm volatile("griddepcontrol.wait;" ::: "memory");
     SA_STAMP(9);
     // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
     Frag first[STAGES + 1];
 #pragma unroll
     for (int s = 0; s <= STAGES; ++s) first[s] = lookup(next_tile());  // all table loads in flight together
+    if (lookups_first) asm volatile("griddepcontrol.wait;" ::: "memory");
     int xq[STAGES];  // tiles in the ring, oldest first
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
