@@ -15,15 +15,17 @@ latency model of the kernel fitted to a sweep on a B200 (batch 1-8, 128-1024 see
 tokens, 1-16 CTAs per pair; the model picks the fastest measured grid on every
 cell of that sweep):
 
-``t = T0 + rounds * T_ROUND + tiles_per_cta * T_TILE + partition(chunks) + merge(chunks)``
+``t = T0 + rounds * T_ROUND + tiles_per_cta * T_TILE + straddle(chunks) + merge(chunks)``
 
 * a CTA has 8 warps with one 16 KB K+V tile in flight each, so it needs
   ``rounds = ceil(tiles_per_cta / 8)`` trips to HBM (``T_ROUND`` each) and moves
   its tiles at about 110 GB/s per SM (``T_TILE`` per tile);
-* from four CTAs per pair on, the kernel snaps the CTAs' slices to pair boundaries,
-  which costs half a microsecond at the head of the launch; with two or three it
-  cuts the tile list into equal slices, and unless a pair's tiles divide evenly one
-  CTA then straddles two pairs and flushes its state twice (``STRADDLE_US``);
+* with two or three CTAs per pair the kernel cuts the tile list into equal slices,
+  and unless a pair's tiles divide evenly one CTA then straddles two pairs and
+  flushes its state twice (``STRADDLE_US``); from four CTAs per pair on, the slices
+  are snapped to pair boundaries.  Either way the partition is worked out before
+  the launch's dependency wait, i.e. while the previous kernel of the stream drains,
+  and costs nothing in a decode loop;
 * more than one CTA per pair adds the in-launch merge of their split states: a
   ticket, one round trip to L2 for the states (the merging CTA asks for 3, 6 or 10
   states per thread, whichever covers the pair; more states take further round
@@ -43,14 +45,13 @@ B200_SM_COUNT = 148
 TILE_BYTES = 16384          # one K tile + one V tile of the streaming kernel
 WARPS_PER_CTA = 8
 # Fitted constants, microseconds (B200, SM clock 1965 MHz, programmatic dependent launch on).
-T0_US = 3.5                 # launch, set-up, first request leaves the SM, output store
+T0_US = 3.0                 # launch, what is left of the set-up after the dependency wait, output store
 T_ROUND_US = 0.9            # one more dependent trip to HBM for a warp
 T_TILE_US = 0.15            # 16 KB through one SM
 ALIGNED_CHUNKS = 4          # CTAs per pair from which the slices are snapped to pair boundaries
-ALIGNED_US = 0.5            # ... and what working that partition out costs
 STRADDLE_US = 3.5           # equal slices that do not end on pair boundaries: a CTA flushes twice
-MERGE_TIERS_US = ((3, 1.8), (6, 2.35), (10, 3.0))  # (states per thread the batch covers, cost)
-MERGE_EXTRA_PASS_US = 1.9   # per further batch of split states the merging CTA has to request
+MERGE_TIERS_US = ((3, 1.8), (6, 2.2), (10, 2.75))  # (states per thread the batch covers, cost)
+MERGE_EXTRA_PASS_US = 2.2   # per further batch of split states the merging CTA has to request
 MERGE_STATES_PER_THREAD = MERGE_TIERS_US[-1][0]
 
 
@@ -194,9 +195,7 @@ def predicted_seed_decode_us(shape: SeedKernelShape, chunks: int) -> float:
     rounds = math.ceil(tiles_per_cta / WARPS_PER_CTA)
     t = T0_US + rounds * T_ROUND_US + tiles_per_cta * T_TILE_US
     if chunks > 1:
-        if chunks >= ALIGNED_CHUNKS:
-            t += ALIGNED_US
-        elif shape.tiles_per_pair % chunks:
+        if chunks < ALIGNED_CHUNKS and shape.tiles_per_pair % chunks:
             t += STRADDLE_US
         # 256 threads share the (head row, 4 columns) work items of the group; each requests the
         # states of its item in batches sized to the pair.
