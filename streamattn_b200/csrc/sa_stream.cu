@@ -391,6 +391,32 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsig
     }
 }
 
+// Row length read as a hint before the launch's dependency wait: a gpu-scope load, served by
+// the L2 (an L1 line allocated now could be stale after the wait).  Same clamping as row_vlen().
+__device__ __forceinline__ int64_t row_vlen_hint(const SeqDesc &s, int b)
+{
+    if (s.mode == kBlocks) return s.blocks_vlen;
+    const int64_t cap = s.mode == kPaged ? static_cast<int64_t>(s.max_pages) * s.page_size : s.kv_len;
+    int64_t n = cap;
+    if (s.seq_lens != nullptr) {
+        if (s.lens_i64) {
+            asm volatile("ld.relaxed.gpu.global.s64 %0, [%1];"
+                         : "=l"(n)
+                         : "l"(static_cast<const int64_t *>(s.seq_lens) + b)
+                         : "memory");
+        } else {
+            int v;
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];"
+                         : "=r"(v)
+                         : "l"(static_cast<const int32_t *>(s.seq_lens) + b)
+                         : "memory");
+            n = v;
+        }
+    }
+    if (n < 0) n = 0;
+    return n < cap ? n : cap;
+}
+
 // Exact merge of the `nseg` split states of one (row, kv head) pair by all threads of the
 // last CTA to arrive on it (items <= NTHREADS).  A work item is 4 columns of one head row;
 // NTHREADS / items threads share an item and each takes every (NTHREADS / items)-th state,
@@ -603,68 +629,29 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // grid's CTAs retire, and hold this grid - before its first global-memory access - until
     // everything launched earlier in the stream has completed and is visible.  Stream order is
     // unchanged; only launch latency and whatever runs before the wait overlap the previous
-    // tail.  Rows of one length need nothing from memory to cut the tile list, so for them the
-    // wait comes after the partition (below, in front of the first table look-ups and copies);
-    // ragged rows read their lengths first and wait here.
+    // tail.  What runs before it here is the partition of the tile list, about 1.5 us of
+    // dependent integer arithmetic:
+    //  - rows of one length need nothing from memory for it, so their wait comes after the
+    //    partition (below, in front of the first table look-ups and copies);
+    //  - ragged rows take their lengths as a HINT before the wait (gpu-scope loads that bypass L1:
+    //    an earlier kernel may still be writing them), cut the tile list with it, wait, read the
+    //    lengths again and keep the partition if no row's tile count changed - which is the
+    //    case in all but one of TILE_N decode steps per row, since a row grows by one token per
+    //    step; otherwise the partition is simply made again.  Nothing is copied, written or
+    //    dereferenced on the strength of a hint.  Row subsets read their row list too and do
+    //    not speculate.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (ragged) asm volatile("griddepcontrol.wait;" ::: "memory");
     SA_STAMP(14);
-    if (ragged) {
-        // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
-        const bool subset = p.seq.num_rows >= 0;
-        if (subset) {
-            // Row subset: rows that are not listed keep length -1 (no tiles, output untouched).
-            for (int b = tid; b < p.batch; b += NTHREADS) vlens[b] = -1;
-            __syncthreads();
-            for (int i = tid; i < p.seq.num_rows; i += NTHREADS) {
-                const int64_t r = load_index(p.seq.rows, p.seq.rows_i64, i);
-                if (r >= 0 && r < p.batch) vlens[r] = static_cast<int>(row_vlen(p.seq, static_cast<int>(r)));
-            }
-            __syncthreads();
-        }
-        if (warp == 0) {
-            int running = 0;
-            for (int base = 0; base < p.batch; base += 32) {
-                const int b = base + lane;
-                int x = 0;
-                if (b < p.batch) {
-                    int n;
-                    if (subset) {
-                        n = vlens[b];
-                    } else {
-                        n = static_cast<int>(row_vlen(p.seq, b));  // < 2^31: the host bounds the capacity
-                        vlens[b] = n;
-                    }
-                    x = n > 0 ? (n + TILE_N - 1) / TILE_N : 0;
-                }
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int y = __shfl_up_sync(0xffffffffu, x, o);
-                    if (lane >= o) x += y;
-                }
-                if (b < p.batch) prefix[b + 1] = running + x;
-                running += __shfl_sync(0xffffffffu, x, 31);
-            }
-            if (lane == 0) prefix[0] = 0;
-        }
-        __syncthreads();
-    } else {
-        __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
-    }
-    fence_proxy_async();
-
-    SA_STAMP(8);
     const uint64_t policy = make_evict_first_policy();
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
     // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
     auto tiles_before = [&](int b) -> int { return ragged ? prefix[b] : b * p.uniform_tiles; };
     // Row lengths were read once for the prefix sum; uniform rows need no load at all.
     auto vlen_of = [&](int b) -> int64_t { return ragged ? static_cast<int64_t>(vlens[b]) : row_vlen(p.seq, b); };
-    const int total_tiles = Hkv * tiles_before(p.batch);
+    int total_tiles = 0;  // set by the partition pass below, like q_t and r_t
     // CTA c owns tiles [c*q + min(c, r), (c+1)*q + min(c+1, r)) with q = T / C, r = T % C:
     // the first r CTAs take one extra tile.  owner(x) is the CTA that owns tile x.
-    const unsigned q_t = static_cast<unsigned>(total_tiles) / static_cast<unsigned>(C);
-    const unsigned r_t = static_cast<unsigned>(total_tiles) - q_t * C;
+    unsigned q_t = 0, r_t = 0;
     auto range_lo = [&](unsigned cc) -> int { return static_cast<int>(cc * q_t + (cc < r_t ? cc : r_t)); };
     auto owner = [&](int x) -> int {
         const unsigned ux = static_cast<unsigned>(x);
@@ -689,6 +676,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         pair_start = row_start + kvh * row_tiles;
     };
 
+
     // Partition of the tile list over the CTAs.  A segment boundary inside a CTA stalls its four
     // warps for the flush/combine, so when there are at least four CTAs per (row, kv head) pair
     // the slice boundaries are snapped to pair boundaries ("aligned"): pair p gets the CTAs
@@ -697,104 +685,196 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int num_pairs = p.batch * Hkv;
     int lo = 0, hi = 0;
     int al_first = 0, al_nseg = 0;
-    bool aligned = total_tiles > 0 && 4 * num_pairs <= C &&
-                   static_cast<uint64_t>(C) * static_cast<uint64_t>(total_tiles) < (1ull << 32);
+    bool aligned = false;
     int al_pair = -1, al_start = 0, al_end = 0;  // aligned mode: this CTA's pair and its tile range
     bool dyn = false;                            // the pair's warps share its tiles (cyclic or claims)
     bool dyn_claims = false;                     // ... through the claim counter
     int dyn_chunk = 1;                           // tiles per claim
     int dyn_nw = 0, dyn_gw = 0;                  // warps working on the pair, this warp's index among them
-    if (aligned) {
-        // One pair per lane: lane pp computes cs(pp); cs(pp+1) comes from the neighbour lane.
-        const unsigned half = static_cast<unsigned>(total_tiles) / 2;
-        bool ok = true;
-        int s0 = 0, s1 = 0;
-        unsigned t0 = 0, t1 = 0;
-        for (int base = 0; base < num_pairs && al_pair < 0; base += 31) {
-            const int pp = base + lane;  // lanes 0..30 own a pair, lane 31 only supplies cs(pp) to lane 30
-            unsigned before = static_cast<unsigned>(total_tiles);
-            if (pp < num_pairs) {
-                const int bb = pp / Hkv;
-                const int tb = tiles_before(bb);
-                before = static_cast<unsigned>(Hkv * tb + (pp - bb * Hkv) * (tiles_before(bb + 1) - tb));
-            }
-            const int start = static_cast<int>((static_cast<unsigned>(C) * before + half) /
-                                               static_cast<unsigned>(total_tiles));
-            const int next_start = __shfl_down_sync(0xffffffffu, start, 1);
-            const unsigned next_before = __shfl_down_sync(0xffffffffu, before, 1);
-            const bool owns = lane < 31 && pp < num_pairs;
-            if (owns && next_before > before && next_start <= start) ok = false;
-            const bool hit = owns && c >= start && c < next_start;
-            const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (m != 0u) {
-                const int src = __ffs(m) - 1;
-                al_pair = base + src;
-                s0 = __shfl_sync(0xffffffffu, start, src);
-                s1 = __shfl_sync(0xffffffffu, next_start, src);
-                t0 = __shfl_sync(0xffffffffu, before, src);
-                t1 = __shfl_sync(0xffffffffu, next_before, src);
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-        }
-        // The "every pair with tiles gets a CTA" test must cover all pairs even after the hit.
-        if (ok && num_pairs > 31) {
-            for (int base = 0; base < num_pairs; base += 32) {
-                const int pp = base + lane;
-                if (pp < num_pairs) {
-                    auto before_of = [&](int q) -> unsigned {
-                        if (q >= num_pairs) return static_cast<unsigned>(total_tiles);
-                        const int bb = q / Hkv;
-                        const int tb = tiles_before(bb);
-                        return static_cast<unsigned>(Hkv * tb + (q - bb * Hkv) * (tiles_before(bb + 1) - tb));
-                    };
-                    const unsigned b0 = before_of(pp), b1 = before_of(pp + 1);
-                    const unsigned c0 = (static_cast<unsigned>(C) * b0 + half) / static_cast<unsigned>(total_tiles);
-                    const unsigned c1 = (static_cast<unsigned>(C) * b1 + half) / static_cast<unsigned>(total_tiles);
-                    if (b1 > b0 && c1 <= c0) ok = false;
-                }
-            }
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        aligned = ok && al_pair >= 0;
+    auto cut_tile_list = [&]() {
+        total_tiles = Hkv * tiles_before(p.batch);
+        q_t = static_cast<unsigned>(total_tiles) / static_cast<unsigned>(C);
+        r_t = static_cast<unsigned>(total_tiles) - q_t * C;
+        lo = hi = 0;
+        al_first = al_nseg = 0;
+        al_pair = -1;
+        al_start = al_end = 0;
+        dyn = dyn_claims = false;
+        dyn_chunk = 1;
+        dyn_nw = dyn_gw = 0;
+        aligned = total_tiles > 0 && 4 * num_pairs <= C &&
+                  static_cast<uint64_t>(C) * static_cast<uint64_t>(total_tiles) < (1ull << 32);
         if (aligned) {
-            const unsigned tiles_p = t1 - t0;
-            const unsigned n_p = static_cast<unsigned>(s1 - s0);
-            const unsigned n_eff = n_p < tiles_p ? n_p : tiles_p;  // never more CTAs than tiles
-            const unsigned k = static_cast<unsigned>(c - s0);
-            al_first = s0;
-            al_nseg = static_cast<int>(n_eff);
-            al_start = static_cast<int>(t0);
-            al_end = static_cast<int>(t1);
-            const bool claims = p.schedule == kScheduleClaims;
-            if ((claims || p.schedule == kScheduleCyclic) && n_eff == n_p && tiles_p >= n_p * WARPS * (STAGES + 1)) {
-                // Shared schedules: the pair's warps take tiles round-robin by position - all of
-                // them (cyclic), or only their first STAGES + 1, after which every tile is claimed
-                // from the pair's counter, so a CTA that the memory system serves slowly simply
-                // ends up with fewer tiles.
-                dyn = true;
-                dyn_claims = claims;
-                // One counter serves about 30 claims per microsecond: with many CTAs on a pair a
-                // claim covers several consecutive tiles.
-                dyn_chunk = (static_cast<int>(n_p) + 15) / 16;
-                dyn_nw = static_cast<int>(n_p) * WARPS;
-                dyn_gw = static_cast<int>(k) * WARPS + warp;
-                lo = al_start;
-                hi = al_end;
-            } else if (k < n_eff) {
-                if (tiles_p < (1u << 20)) {  // products fit 32 bits (n_eff <= C <= 4096)
-                    lo = static_cast<int>(t0 + tiles_p * k / n_eff);
-                    hi = static_cast<int>(t0 + tiles_p * (k + 1) / n_eff);
-                } else {
-                    lo = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * k / n_eff));
-                    hi = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * (k + 1) / n_eff));
+            // One pair per lane: lane pp computes cs(pp); cs(pp+1) comes from the neighbour lane.
+            const unsigned half = static_cast<unsigned>(total_tiles) / 2;
+            bool ok = true;
+            int s0 = 0, s1 = 0;
+            unsigned t0 = 0, t1 = 0;
+            for (int base = 0; base < num_pairs && al_pair < 0; base += 31) {
+                const int pp = base + lane;  // lanes 0..30 own a pair, lane 31 only supplies cs(pp) to lane 30
+                unsigned before = static_cast<unsigned>(total_tiles);
+                if (pp < num_pairs) {
+                    const int bb = pp / Hkv;
+                    const int tb = tiles_before(bb);
+                    before = static_cast<unsigned>(Hkv * tb + (pp - bb * Hkv) * (tiles_before(bb + 1) - tb));
+                }
+                const int start = static_cast<int>((static_cast<unsigned>(C) * before + half) /
+                                                   static_cast<unsigned>(total_tiles));
+                const int next_start = __shfl_down_sync(0xffffffffu, start, 1);
+                const unsigned next_before = __shfl_down_sync(0xffffffffu, before, 1);
+                const bool owns = lane < 31 && pp < num_pairs;
+                if (owns && next_before > before && next_start <= start) ok = false;
+                const bool hit = owns && c >= start && c < next_start;
+                const unsigned m = __ballot_sync(0xffffffffu, hit);
+                if (m != 0u) {
+                    const int src = __ffs(m) - 1;
+                    al_pair = base + src;
+                    s0 = __shfl_sync(0xffffffffu, start, src);
+                    s1 = __shfl_sync(0xffffffffu, next_start, src);
+                    t0 = __shfl_sync(0xffffffffu, before, src);
+                    t1 = __shfl_sync(0xffffffffu, next_before, src);
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            // The "every pair with tiles gets a CTA" test must cover all pairs even after the hit.
+            if (ok && num_pairs > 31) {
+                for (int base = 0; base < num_pairs; base += 32) {
+                    const int pp = base + lane;
+                    if (pp < num_pairs) {
+                        auto before_of = [&](int q) -> unsigned {
+                            if (q >= num_pairs) return static_cast<unsigned>(total_tiles);
+                            const int bb = q / Hkv;
+                            const int tb = tiles_before(bb);
+                            return static_cast<unsigned>(Hkv * tb + (q - bb * Hkv) * (tiles_before(bb + 1) - tb));
+                        };
+                        const unsigned b0 = before_of(pp), b1 = before_of(pp + 1);
+                        const unsigned c0 = (static_cast<unsigned>(C) * b0 + half) / static_cast<unsigned>(total_tiles);
+                        const unsigned c1 = (static_cast<unsigned>(C) * b1 + half) / static_cast<unsigned>(total_tiles);
+                        if (b1 > b0 && c1 <= c0) ok = false;
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            aligned = ok && al_pair >= 0;
+            if (aligned) {
+                const unsigned tiles_p = t1 - t0;
+                const unsigned n_p = static_cast<unsigned>(s1 - s0);
+                const unsigned n_eff = n_p < tiles_p ? n_p : tiles_p;  // never more CTAs than tiles
+                const unsigned k = static_cast<unsigned>(c - s0);
+                al_first = s0;
+                al_nseg = static_cast<int>(n_eff);
+                al_start = static_cast<int>(t0);
+                al_end = static_cast<int>(t1);
+                const bool claims = p.schedule == kScheduleClaims;
+                if ((claims || p.schedule == kScheduleCyclic) && n_eff == n_p && tiles_p >= n_p * WARPS * (STAGES + 1)) {
+                    // Shared schedules: the pair's warps take tiles round-robin by position - all of
+                    // them (cyclic), or only their first STAGES + 1, after which every tile is claimed
+                    // from the pair's counter, so a CTA that the memory system serves slowly simply
+                    // ends up with fewer tiles.
+                    dyn = true;
+                    dyn_claims = claims;
+                    // One counter serves about 30 claims per microsecond: with many CTAs on a pair a
+                    // claim covers several consecutive tiles.
+                    dyn_chunk = (static_cast<int>(n_p) + 15) / 16;
+                    dyn_nw = static_cast<int>(n_p) * WARPS;
+                    dyn_gw = static_cast<int>(k) * WARPS + warp;
+                    lo = al_start;
+                    hi = al_end;
+                } else if (k < n_eff) {
+                    if (tiles_p < (1u << 20)) {  // products fit 32 bits (n_eff <= C <= 4096)
+                        lo = static_cast<int>(t0 + tiles_p * k / n_eff);
+                        hi = static_cast<int>(t0 + tiles_p * (k + 1) / n_eff);
+                    } else {
+                        lo = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * k / n_eff));
+                        hi = static_cast<int>(t0 + static_cast<unsigned>(static_cast<uint64_t>(tiles_p) * (k + 1) / n_eff));
+                    }
                 }
             }
         }
+        if (!aligned) {
+            lo = range_lo(c);
+            hi = range_lo(c + 1);
+        }
+    };
+    const bool speculate = ragged && p.seq.num_rows < 0;
+    bool waited = false;
+    if (!ragged) {  // rows of one length: one pass, nothing to read
+        __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
+        fence_proxy_async();
+        SA_STAMP(8);
+        cut_tile_list();
     }
-    if (!aligned) {
-        lo = range_lo(c);
-        hi = range_lo(c + 1);
+#pragma unroll 1
+    for (int pass = 0; ragged && pass < 2; ++pass) {
+        const bool hint = speculate && pass == 0;
+        if (!hint && !waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
+        {
+            // Tiles per row depend on lengths that live on the device: prefix-sum them once per CTA.
+            const bool subset = p.seq.num_rows >= 0;
+            if (subset) {
+                // Row subset: rows that are not listed keep length -1 (no tiles, output untouched).
+                for (int b = tid; b < p.batch; b += NTHREADS) vlens[b] = -1;
+                __syncthreads();
+                for (int i = tid; i < p.seq.num_rows; i += NTHREADS) {
+                    const int64_t r = load_index(p.seq.rows, p.seq.rows_i64, i);
+                    if (r >= 0 && r < p.batch) vlens[r] = static_cast<int>(row_vlen(p.seq, static_cast<int>(r)));
+                }
+                __syncthreads();
+            }
+            if (warp == 0) {
+                int running = 0;
+                for (int base = 0; base < p.batch; base += 32) {
+                    const int b = base + lane;
+                    int x = 0;
+                    if (b < p.batch) {
+                        int n;
+                        if (subset) {
+                            n = vlens[b];
+                        } else {
+                            // < 2^31: the host bounds the capacity
+                            n = static_cast<int>(hint ? row_vlen_hint(p.seq, b) : row_vlen(p.seq, b));
+                            vlens[b] = n;
+                        }
+                        x = n > 0 ? (n + TILE_N - 1) / TILE_N : 0;
+                    }
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int y = __shfl_up_sync(0xffffffffu, x, o);
+                        if (lane >= o) x += y;
+                    }
+                    if (b < p.batch) prefix[b + 1] = running + x;
+                    running += __shfl_sync(0xffffffffu, x, 31);
+                }
+                if (lane == 0) prefix[0] = 0;
+            }
+            __syncthreads();
+        }
+        if (pass == 0) fence_proxy_async();
+        SA_STAMP(8);
+
+        cut_tile_list();
+        if (!hint) break;
+        // The partition above rests on a hint: wait, read the lengths for good, compare.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        waited = true;
+        bool same = true;
+        int fresh = 0;
+        if (tid < p.batch) {  // one row per thread; larger batches do not use the hint (below)
+            fresh = static_cast<int>(row_vlen(p.seq, tid));
+            const int tiles = fresh > 0 ? (fresh + TILE_N - 1) / TILE_N : 0;
+            same = tiles == prefix[tid + 1] - prefix[tid];
+        }
+        if (p.batch > NTHREADS) same = false;
+        same = __syncthreads_and(same);  // also: every warp is done reading the hinted lengths
+        if (same) {
+            if (tid < p.batch) vlens[tid] = fresh;  // the lengths proper (masks of the rows' last tiles)
+            __syncthreads();
+            break;
+        }
     }
     // Static schedule: this warp's tiles are lo + warp + i*WARPS for i in [0, n_w), across all
     // segments of the CTA, so its copy pipeline keeps running through segment boundaries.

@@ -260,3 +260,50 @@ def test_bound_append_plan_and_decode_replay_in_a_cuda_graph(dev):
                                    want_v[:, :, :n].transpose(1, 2).contiguous())
     diff = (plan.output.float().cpu() - want.float()).abs()
     assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3
+
+
+def test_back_to_back_steps_that_cross_tile_boundaries_match_the_oracle(dev):
+    """Append + decode steps launched back to back, with no host synchronisation in between, while
+    rows grow across multiples of the kernel's 128-token tile.
+
+    The decode kernel cuts its tile list before the launch's dependency wait from row lengths that
+    the append kernel in front of it may still be writing, and checks them after the wait: a row
+    whose tile count changed must make it cut the list again.  Every step's output is compared
+    with the oracle's loop."""
+
+    g = torch.Generator().manual_seed(91)
+    batch, q_heads, kv_heads, dim, cap, steps = 3, 8, 2, 64, 512, 7
+    start = [126, 254, 40]                   # rows 0 and 1 cross 128 / 256 at steps 3 and 2
+    k = torch.randn(batch, kv_heads, cap, dim, generator=g).bfloat16()
+    v = torch.randn(batch, kv_heads, cap, dim, generator=g).bfloat16()
+    q_raw = torch.randn(batch, 1, q_heads, dim, generator=g).bfloat16()      # [B, 1, Hq, D]
+    k_new = torch.randn(batch, kv_heads, 1, dim, generator=g).bfloat16()
+    v_new = torch.randn(batch, kv_heads, 1, dim, generator=g).bfloat16()
+    angles = torch.randn(batch, 1, dim // 2, generator=g)
+    emb = torch.cat((angles, angles), dim=-1)
+    cos, sin = emb.cos().bfloat16(), emb.sin().bfloat16()
+
+    kd, vd = k.to(dev), v.to(dev)
+    lens = torch.tensor(start, dtype=torch.int32, device=dev)
+    q_rot = torch.empty(batch, 1, q_heads, dim, dtype=torch.bfloat16, device=dev)
+    plan = sa.ExactDecodePlan.build(q_rot, kd, vd, kv_layout="BHND", seq_lens=lens)
+    append = sa.AppendKVPlan.build(kd, vd, k_new.to(dev), v_new.to(dev), lens, kv_layout="BHND", cos=cos.to(dev),
+                                   sin=sin.to(dev), query=q_raw.to(dev), query_out=q_rot, query_layout="BNHD",
+                                   lengths_out=lens)
+    outs = torch.empty(steps, batch, 1, q_heads, dim, dtype=torch.bfloat16, device=dev)
+    for step in range(steps):                # no host sync: the launches queue up behind one another
+        append.run()
+        outs[step].copy_(plan.run())
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    assert lens.cpu().tolist() == [n + steps for n in start]
+
+    ref_k, ref_v, lengths = k.clone(), v.clone(), list(start)
+    for step in range(steps):
+        want_q = torch_port.rope_append(q_raw.transpose(1, 2), k_new, v_new, cos, sin, ref_k, ref_v, lengths)
+        lengths = [n + 1 for n in lengths]
+        want = cpu_oracle.exact_decode(want_q.transpose(1, 2).contiguous(), ref_k, ref_v, kv_layout="BHND",
+                                       lengths=torch.tensor(lengths, dtype=torch.int32))
+        diff = (outs[step].float().cpu() - want.float()).abs()
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3, (step, lengths, float(diff.max()))
+    assert torch.equal(kd.cpu(), ref_k) and torch.equal(vd.cpu(), ref_v)
