@@ -60,7 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 f"({LIB_PATH}) and has no CPU or interpreted fallback"
             )
         LIB_DIR.mkdir(parents=True, exist_ok=True)
-        tmp = LIB_PATH.with_suffix(".so.tmp")
+        # One temporary per process: several ranks may find the library stale at the same time.
+        tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
         cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), *[str(p) for p in source_files()]]
         if verbose:
             cmd.insert(1, "-Xptxas")

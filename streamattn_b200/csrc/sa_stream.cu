@@ -109,12 +109,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
+#ifdef SA_TIMELINE
 __device__ __forceinline__ unsigned sm_id()
 {
     unsigned id;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(id));
     return id;
 }
+#endif
 
 __device__ __forceinline__ unsigned long long global_timer_ns()
 {
