@@ -59,7 +59,7 @@ struct StreamParams {
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
-    unsigned long long *timeline;  // instrumented builds only: 16 words (globaltimer stamps, SM, poll count) per CTA
+    unsigned long long *timeline;  // instrumented builds only: 16 words (globaltimer stamps, SM id) per CTA
 #endif
 };
 
@@ -70,16 +70,6 @@ struct StreamParams {
 #define SA_STAMP_VALUE(i, v) do { } while (0)
 #endif
 #define SA_STAMP(i) SA_STAMP_VALUE(i, global_timer_ns())
-// The merge is out of line: instrumented builds hand it the CTA's row of the stamp buffer.
-#ifdef SA_TIMELINE
-#define SA_TL_PARAM , unsigned long long *tl_row
-#define SA_TL_ARG , (p.timeline != nullptr ? p.timeline + blockIdx.x * 16 : nullptr)
-#define SA_TL_STAMP(i) do { if (tl_row != nullptr && tid == 0) tl_row[i] = global_timer_ns(); } while (0)
-#else
-#define SA_TL_PARAM
-#define SA_TL_ARG
-#define SA_TL_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -434,15 +424,13 @@ __device__ __forceinline__ int64_t row_vlen_hint(const SeqDesc &s, int b)
 // storing its state: the wait is for a few hundred nanoseconds of work of CTAs that are already
 // running, never for a CTA that still has to be scheduled.  The per-thread results meet in shared
 // memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l) and all nseg states are zero
-// again.  Returns how often this thread had to ask again.  Out of line so that the rows in
-// flight do not weigh on the streaming loop's registers.
+// again.  Out of line so that the rows in flight do not weigh on the streaming loop's registers.
 template <int D, int NTHREADS, int BATCH>
-__device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
+__device__ __noinline__ void merge_pair_states(float *first_slot, int64_t slot_stride, int nseg, int self,
                                               const float *own, int items, float *sm, int tid,
-                                              unsigned long long wait_ns, int *status SA_TL_PARAM)
+                                              unsigned long long wait_ns, int *status)
 {
     constexpr int PART_STRIDE = D + 4;
-    SA_TL_STAMP(10);
     // Small non-negative integers: floor(a / b) = floor((a + 0.5) * (1 / b)) without the long
     // integer-division sequence (the half keeps the product clear of the next integer).
     const float inv_items = __frcp_rn(static_cast<float>(items));
@@ -490,7 +478,6 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
                 }
             }
         }
-        SA_TL_STAMP(11);
         {   // the CTA's own state takes its place in the sequence (stored like the others)
             const float *mine = own + item * 6;
 #pragma unroll
@@ -529,7 +516,6 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
     __syncthreads();  // every thread has read its states: they can be cleared
-    SA_TL_STAMP(12);
     if (active) {
         for (int i = part; i < nseg; i += parts) {
             // Plain stores: the next reader is a later launch, which the launch boundary orders.
@@ -556,8 +542,6 @@ __device__ __noinline__ int merge_pair_states(float *first_slot, int64_t slot_st
         *reinterpret_cast<float2 *>(mine + 4) = make_float2(big, total_l);
     }
     __syncthreads();
-    SA_TL_STAMP(13);
-    return static_cast<int>(polls);
 }
 
 // One fragment (TMA box) of a tile as seen by the issuing lane.
@@ -643,7 +627,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     //    dereferenced on the strength of a hint.  Row subsets read their row list too and do
     //    not speculate.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    SA_STAMP(14);
     const uint64_t policy = make_evict_first_policy();
     // Tile indices fit in 32 bits (the host checks the total); only products with the CTA
     // count need 64 bits.  32-bit divisions keep the per-tile bookkeeping cheap.
@@ -804,7 +787,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     if (!ragged) {  // rows of one length: one pass, nothing to read
         __syncwarp();  // this warp's barriers are initialised; nothing else is shared yet
         fence_proxy_async();
-        SA_STAMP(8);
         cut_tile_list();
     }
 #pragma unroll 1
@@ -856,7 +838,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             __syncthreads();
         }
         if (pass == 0) fence_proxy_async();
-        SA_STAMP(8);
 
         cut_tile_list();
         if (!hint) break;
@@ -1011,7 +992,6 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // block lists, no claim counter) - after that as well.
     const bool lookups_first = !ragged && p.seq.blocks_dev == nullptr && !dyn_claims;
     if (!ragged && !lookups_first) asm volatile("griddepcontrol.wait;" ::: "memory");
-    SA_STAMP(9);
     // Fill the ring before anything else so HBM is busy while the rest of the prologue runs.
     Frag first[STAGES + 1];
 #pragma unroll
@@ -1404,23 +1384,15 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                         (static_cast<float>(nseg + sharers - 1) + 0.5f) * __frcp_rn(static_cast<float>(sharers)));
                     float *slots = first_slot + r0 * PART_STRIDE;
                     const float *mine = states + k * NTHREADS * 6;
-                    int polls;
                     if (per_thread <= 3)
-                        polls = merge_pair_states<D, NTHREADS, 3>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                  sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
+                        merge_pair_states<D, NTHREADS, 3>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
                     else if (per_thread <= 6)
-                        polls = merge_pair_states<D, NTHREADS, 6>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                  sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
+                        merge_pair_states<D, NTHREADS, 6>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                  sub_items, scratch, tid, p.wait_ns, p.status);
                     else
-                        polls = merge_pair_states<D, NTHREADS, 10>(slots, slot_stride, nseg, c - first_cta, mine,
-                                                                   sub_items, scratch, tid, p.wait_ns, p.status SA_TL_ARG);
-#ifdef SA_TIMELINE
-                    {
-                        const int most = __reduce_max_sync(0xffffffffu, polls);  // of warp 0
-                        SA_STAMP_VALUE(7, 1000 + most);
-                    }
-#endif
-                    (void)polls;
+                        merge_pair_states<D, NTHREADS, 10>(slots, slot_stride, nseg, c - first_cta, mine,
+                                                                   sub_items, scratch, tid, p.wait_ns, p.status);
                     if (tid < sub_items) {
                         const int row = tid / (D / 4);
                         const float *r = scratch + tid * 6;
