@@ -291,6 +291,7 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsig
     const size_t rank_stride = total_rows * STATE_STRIDE;
     const int parts = items <= NTHREADS ? NTHREADS / items : 1;
     const unsigned long long t0 = global_timer_ns();
+    unsigned polls = 0;
     for (int first = 0; first < items; first += NTHREADS) {  // a single pass unless items > NTHREADS
         const int part = parts > 1 ? tid / items : 0;
         const int item = parts > 1 ? tid - part * items : first + tid;
@@ -323,7 +324,8 @@ __device__ __noinline__ void cp_finish_pair(const CpFuse &cp, int *status, unsig
                             landed &= static_cast<uint32_t>(static_cast<uint32_t>(w[u][j].x >> 32) == cp.step) &
                                       static_cast<uint32_t>(static_cast<uint32_t>(w[u][j].y >> 32) == cp.step);
                     waiting = landed == 0u;
-                    if (waiting && global_timer_ns() - t0 > wait_ns) {
+                    // The clock is slow to read: look at it every 16th round of loads.
+                    if (waiting && (++polls & 15u) == 0u && global_timer_ns() - t0 > wait_ns) {
                         atomicOr(status, SA_DEV_PIPELINE_TIMEOUT);
                         break;
                     }
