@@ -29,7 +29,9 @@ microseconds per call over the repeats (the reference times its kernels the same
 benchmarks/profile_paged_exact_decode.py:284-309).  At N=1 the line also carries a
 ``secondary`` list with the other configurations (paged, seed-only, BNHD, decode loop and
 the 1M-token row on one GPU - the base of the strong-scaling series), each with its own
-protocol timing, roofline figures, end-to-end time and clock record.
+protocol timing, roofline figures, end-to-end time and clock record, and an entry
+``exact_c2_plain_launch``: config 2 timed in a child process without programmatic dependent
+launch, i.e. with nothing of a call overlapping the call before it.
 """
 
 from __future__ import annotations
@@ -38,6 +40,7 @@ import argparse
 import json
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
@@ -516,6 +519,29 @@ def make_e2e(workload: str, case, device):
     return step, "pinned-host query copied in, output copied out (two async copies around run())", q_host, out_host
 
 
+def measure_without_launch_overlap() -> dict:
+    """Config 2 once more in a child process with programmatic dependent launch switched off.
+
+    Back-to-back calls normally overlap the head of a launch (set-up, the partition of the tile
+    list) with the tail of the launch before it; the switch is read once per process, hence the
+    child.  The difference to the headline figure is what that overlap is worth.
+    """
+
+    env = dict(os.environ, STREAMATTN_B200_NO_PDL="1")
+    cmd = [sys.executable, os.path.abspath(__file__), "--workload", "exact_c2", "--profile", "--steps", "1000",
+           "--warmup", "50"]
+    entry = {"workload": "exact_c2_plain_launch",
+             "note": "config 2 with STREAMATTN_B200_NO_PDL=1 (plain stream serialization): nothing of a launch "
+                     "overlaps the launch before it; one region of 1000 back-to-back calls in a child process"}
+    try:
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+        lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+        entry["us_per_call"] = json.loads(lines[-1])["us_per_call"]
+    except Exception as exc:  # the figure is informative: the line must not depend on it
+        entry["error"] = f"{type(exc).__name__}: {exc}"[:200]
+    return entry
+
+
 def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, steps: int, warmup: int,
                  headline: bool) -> dict:
     """All figures of one workload: --steps region (headline only), protocol timing, e2e, roofline, clocks."""
@@ -902,6 +928,7 @@ def main() -> None:
     if world == 1 and workload == "exact_c2" and not args.no_secondary:
         extras = [measure_seed_grid(device), measure_o_proj(device)]
         torch.cuda.empty_cache()
+        extras.append(measure_without_launch_overlap())
     clocks.stop()
     for entry in [head, *secondary]:
         entry["clocks"] = clocks.summary(*entry.pop("clock_window"))
