@@ -228,6 +228,15 @@ bool build_stream_geometry(const Problem &p, int64_t max_vlen, StreamGeometry *g
     // memory: there the CTAs of a pair take tiles round-robin, so all heads of a row sweep the
     // same addresses together; head-major caches give every CTA one contiguous slice.
     geo->schedule = geo->tok_dim == 2 ? kScheduleCyclic : kScheduleBlocked;
+    // Who merges the split states of a pair: its first CTA, which looks until the states of the
+    // others have landed - no arrival ticket, whose round trip would sit between the last CTA's
+    // last tile and the merge (measured: paged config 3 31.9 -> 31.1 us, config 2 42.5 -> 42.1).
+    // The first CTA may be waiting for CTAs that are still to be scheduled, so every CTA of the
+    // grid must be able to be resident at once (one per SM); a larger grid, which only an
+    // explicit CTA count can ask for, elects the last arriver by ticket instead.
+    const char *force = std::getenv("STREAMATTN_B200_MERGER");  // "ticket": the other form, for A/B timing
+    geo->first_merges = ctas <= (p.sm_count > 0 ? p.sm_count : 148);
+    if (force != nullptr && std::strcmp(force, "ticket") == 0) geo->first_merges = 0;
     return true;
 }
 

@@ -56,6 +56,7 @@ struct StreamParams {
     int schedule;        // kScheduleBlocked / kScheduleCyclic / kScheduleClaims
     int kv_split;        // virtual KV heads per physical KV head (kv_heads and group above are virtual)
     unsigned long long wait_ns;  // limit of every bounded wait
+    int first_merges;    // the pair's first CTA merges its split states (no ticket): grids of at most one CTA per SM
     SeqDesc seq;
     CpFuse cp;           // context-parallel exchange fused into this launch (cp.world == 0: off)
 #ifdef SA_TIMELINE
@@ -421,10 +422,12 @@ __device__ __forceinline__ int64_t row_vlen_hint(const SeqDesc &s, int b)
 // sum at its index position, so the order of the additions - and with it every bit of the result
 // - does not depend on which CTA happens to arrive last.
 // The other states are published with inverted bits (see state_load4): a word that still reads
-// zero has not landed yet and the batch is requested again, for at most `wait_ns`.  Every other
-// CTA of the pair took its ticket earlier, i.e. has left its streaming loop and is combining and
-// storing its state: the wait is for a few hundred nanoseconds of work of CTAs that are already
-// running, never for a CTA that still has to be scheduled.  The per-thread results meet in shared
+// zero has not landed yet and the batch is requested again, for at most `wait_ns`.  The merging
+// CTA is the pair's first one when the whole grid can be resident at once: it may then be looking
+// for microseconds, until the slowest CTA of the pair has stored its state.  In a larger grid it
+// is the last CTA to take the pair's ticket: every other CTA has then left its streaming loop,
+// and the wait is for a few hundred nanoseconds of work of CTAs that are already running, never
+// for a CTA that still has to be scheduled.  The per-thread results meet in shared
 // memory; on return sm[item * 6 ..] = (o[4] unnormalised, m, l) and all nseg states are zero
 // again.  Out of line so that the rows in flight do not weigh on the streaming loop's registers.
 template <int D, int NTHREADS, int BATCH>
@@ -1304,8 +1307,12 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         // nothing, and its round trip overlaps the combine below.  (Asking for it earlier still -
         // when the last tile of warp 0 lands, or right after the tile loop - measured slower: the
         // merger then looks before the last states have landed and pays a second round trip.)
+        // That is the form for grids larger than the GPU.  When every CTA can be resident at once
+        // (p.first_merges) there is no ticket at all: the pair's first CTA merges, whenever it is
+        // done itself, and simply looks until the others' states have landed - the last CTA to
+        // finish only has to store its state.
         int old_count = 0;
-        if (nseg > 1 && tid == 0)
+        if (nseg > 1 && tid == 0 && !p.first_merges)
             asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], 1;"
                          : "=r"(old_count)
                          : "l"(p.counters + pair)
@@ -1367,7 +1374,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     *reinterpret_cast<float2 *>(dst + 4) = make_float2(own[k][4], own[k][5]);
                 }
             }
-            if (tid == 0) s_last = old_count == nseg - 1;
+            if (tid == 0) s_last = p.first_merges ? c == first_cta : old_count == nseg - 1;
             __syncthreads();
             SA_STAMP(5);
             if (s_last) {
@@ -1404,7 +1411,7 @@ stream_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     __syncthreads();  // the scratch is reused by the next rows
                 }
                 if (tid == 0) {  // ready for the next launch: every CTA of the pair has arrived
-                    p.counters[pair] = 0;
+                    if (!p.first_merges) p.counters[pair] = 0;
                     if (dyn_claims) p.pool[pair] = 0;
                 }
             }
@@ -1539,6 +1546,7 @@ cudaError_t launch_stream(const Problem &p, const StreamGeometry &geo, const CpF
     sp.uniform_tiles = p.seq.num_rows >= 0 ? -1 : geo.uniform_tiles;
     sp.schedule = geo.schedule;
     sp.wait_ns = p.wait_ns;
+    sp.first_merges = geo.first_merges;
     sp.seq = p.seq;
     sp.cp = cp;
 #ifdef SA_TIMELINE

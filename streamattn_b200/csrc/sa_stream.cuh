@@ -47,6 +47,7 @@ struct StreamGeometry {
     int num_ctas;
     int kv_split;        // groups of more than 16 query heads: virtual KV heads per physical one (else 1)
     int schedule;        // how the CTAs of one (row, kv head) pair share its tiles (kSchedule*)
+    int first_merges;    // a pair's first CTA merges its split states (grids of at most one CTA per SM); else a ticket elects the last arriver
 };
 
 // Smallest s with group % s == 0 and group / s <= 16 (0 if there is none): a KV head with more
