@@ -26,8 +26,8 @@ cell of that sweep):
   are snapped to pair boundaries.  Either way the partition is worked out before
   the launch's dependency wait, i.e. while the previous kernel of the stream drains,
   and costs nothing in a decode loop;
-* more than one CTA per pair adds the in-launch merge of their split states: a
-  ticket, one round trip to L2 for the states (the merging CTA asks for 3, 6 or 10
+* more than one CTA per pair adds the in-launch merge of their split states by the
+  pair's first CTA: one round trip to L2 for the states (the merging CTA asks for 3, 6 or 10
   states per thread, whichever covers the pair; more states take further round
   trips), the output store.
 
