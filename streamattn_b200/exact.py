@@ -63,7 +63,7 @@ class ExactDecodePlan:
         (row, KV head); ``None`` sizes the grid to the GPU.  ``promoted_only``
         is accepted for compatibility and has no effect: every supported shape
         is served.  ``dynamic_schedule=True`` lets the CTAs of a (row, KV head)
-        pair claim tiles from a device counter (a few percent faster when HBM
+        pair claim tiles from a device counter (up to 3 % faster when HBM
         bound; results stay within tolerance but are no longer bit-identical
         from launch to launch); ``None`` follows ``STREAMATTN_B200_SCHEDULE``.
         ``row_indices`` (device int32/int64 tensor, read at run time) restricts the
