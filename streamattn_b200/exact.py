@@ -64,7 +64,7 @@ class ExactDecodePlan:
         is accepted for compatibility and has no effect: every supported shape
         is served.  ``dynamic_schedule=True`` lets the CTAs of a (row, KV head)
         pair claim tiles from a device counter (up to 3 % faster when HBM
-        bound; results stay within tolerance but are no longer bit-identical
+        bound, in some runs slower: measure; results stay within tolerance but are no longer bit-identical
         from launch to launch); ``None`` follows ``STREAMATTN_B200_SCHEDULE``.
         ``row_indices`` (device int32/int64 tensor, read at run time) restricts the
         plan to those batch rows: the output rows of all other rows stay untouched

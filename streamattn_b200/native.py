@@ -358,7 +358,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 def dynamic_default() -> bool:
     """Whether plans use the dynamic tile schedule when the caller does not say.
 
-    ``STREAMATTN_B200_SCHEDULE=dynamic`` turns it on: up to 3 % faster on HBM-bound calls,
+    ``STREAMATTN_B200_SCHEDULE=dynamic`` turns it on: up to 3 % faster on HBM-bound calls (in some runs slower),
     results within tolerance but no longer bit-identical from one launch to the next.
     """
 
