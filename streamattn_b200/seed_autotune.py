@@ -12,8 +12,8 @@ once per KV head and shares it among the query heads of the group, so the only
 thing left to choose is how many CTAs work on one (row, KV head) pair.  A
 candidate is therefore "``seed_chunks`` CTAs per pair"; its cost comes from a
 latency model of the kernel fitted to a sweep on a B200 (batch 1-8, 128-1024 seed
-tokens, 1-16 CTAs per pair; the model picks the fastest measured grid on every
-cell of that sweep):
+tokens, 1-16 CTAs per pair; the model's grid is the fastest measured one, or within
+4 % of it, on every cell of that sweep):
 
 ``t = T0 + rounds * T_ROUND + tiles_per_cta * T_TILE + straddle(chunks) + merge(chunks)``
 
