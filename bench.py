@@ -29,7 +29,8 @@ microseconds per call over the repeats (the reference times its kernels the same
 benchmarks/profile_paged_exact_decode.py:284-309).  At N=1 the line also carries a
 ``secondary`` list with the other configurations (paged, seed-only, BNHD, decode loop and
 the 1M-token row on one GPU - the base of the strong-scaling series), each with its own
-protocol timing, roofline figures, end-to-end time and clock record, and an entry
+protocol timing, roofline figures, end-to-end time, the time per call under CUDA-graph replay
+(``graph_replay``: 20 calls per graph) and clock record, and an entry
 ``exact_c2_plain_launch``: config 2 timed in a child process without programmatic dependent
 launch, i.e. with nothing of a call overlapping the call before it.
 """
@@ -542,6 +543,40 @@ def measure_without_launch_overlap() -> dict:
     return entry
 
 
+def graph_replay_time(run, device, calls: int = 20, replays: int = 10, repeats: int = 9) -> dict:
+    """Microseconds per call when ``calls`` consecutive calls are captured into one CUDA graph and
+    the graph is replayed (the reference also times its decode plans under graph replay).
+
+    Median over ``repeats`` regions of ``replays`` replays each, every region between its own pair
+    of CUDA events.  The loop workload is left out by its caller: its cache grows with every call.
+    """
+
+    side = torch.cuda.Stream(device=device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            run()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(calls):
+                run()
+    torch.cuda.synchronize(device)
+    for _ in range(3):
+        graph.replay()
+    times = []
+    for _ in range(repeats):
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize(device)
+        times.append(start.elapsed_time(stop) * 1e3 / (replays * calls))
+    return {"us_per_call": statistics.median(times), "min_us": min(times), "max_us": max(times),
+            "calls_per_graph": calls, "replays_per_repeat": replays, "repeats": repeats}
+
+
 def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, steps: int, warmup: int,
                  headline: bool) -> dict:
     """All figures of one workload: --steps region (headline only), protocol timing, e2e, roofline, clocks."""
@@ -576,6 +611,15 @@ def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, ste
         run()
         torch.cuda.synchronize(device)
         torch.testing.assert_close(out_host.float(), case["out"].float().cpu(), atol=2e-2, rtol=0)
+    # The same call captured into a CUDA graph (not the loop, whose cache grows with every call,
+    # nor the fused context-parallel plan, whose step number is a launch argument).
+    graph = None
+    if workload not in ("loop_c2", "cp_c5"):
+        try:
+            graph = graph_replay_time(run, device)
+        except Exception as exc:  # informative figure: the line must not depend on it
+            graph = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            torch.cuda.synchronize(device)
     us = proto["us_per_call"]
     achieved = per_gpu_bytes / (us * 1e-6) / 1e9
     traffic, traffic_source = traffic_per_launch(workload, world)
@@ -595,6 +639,7 @@ def measure_case(workload: str, case, ranks: Ranks, clocks: ClockSampler, *, ste
                 "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
                 "note": e2e_mode + "; the KV cache is resident device state bound to the plan"},
         "launches_per_call": launches,
+        "graph_replay": graph,
         "clock_window": (t_begin, t_end),
         "device_status": case["plan"].device_status() if hasattr(case["plan"], "device_status") else 0,
     })
@@ -959,6 +1004,7 @@ def main() -> None:
                          "how": "median of 9 repeats, each >= 200 calls between one pair of CUDA events, after "
                                 ">= 20 warm-up calls; max over ranks per repeat"},
             "e2e": head["e2e"],
+            "graph_replay": head.get("graph_replay"),
             "gpu_launches": args.steps * launches,
             "clocks": head["clocks"],
             "device_status": head["device_status"],
