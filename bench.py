@@ -780,7 +780,26 @@ def measure_o_proj(device) -> dict:
     chain_us = quick_time(chain, device)
     chain_late_us = quick_time(chain_late, device)
     cold_gbs = alg / (cold["us_per_call"] * 1e-6) / 1e9
+    # The same projection behind the decode-loop step of config 2 (append + decode; 16 heads x 64
+    # = 1024 input features, 2048 outputs): three launches per step on one stream.
+    del case
+    torch.cuda.empty_cache()
+    loop = build_loop_c2(device)
+    weight_c2 = (_randn_bf16((hidden, 1024), 71, device).float() / 16.0).bfloat16()
+    proj_c2 = sa.OProjPlan.build(loop["out"].view(B, 1, 1024), weight_c2)
+    loop_step = loop["run"]
+
+    def loop_chain():
+        loop_step()
+        return proj_c2.run()
+
+    loop_us = quick_time(loop_step, device)
+    loop_chain_us = quick_time(loop_chain, device)
+    del loop
+    torch.cuda.empty_cache()
     return {"workload": "o_proj_qwen3b", "batch": B, "in_features": hidden, "out_features": hidden,
+            "loop_c2_us": loop_us, "loop_c2_then_o_proj_us": loop_chain_us,
+            "loop_c2_o_proj_visible_us": loop_chain_us - loop_us,
             "algorithmic_bytes": alg, "us_per_call_l2_warm": alone, "cold_l2": cold,
             "roofline_cold": {"bound": "hbm", "achieved": cold_gbs, "peak": peak, "unit": "GB/s",
                               "frac": cold_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth",
