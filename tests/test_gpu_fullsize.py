@@ -203,3 +203,29 @@ def test_config5_shape_family_d128_g4_long_context(dev):
     merged = torch.empty_like(q)
     native.merge_states(torch.stack(states).contiguous(), merged)
     _close(merged, want)
+
+
+def test_result_bits_do_not_depend_on_which_cta_merges(dev, monkeypatch):
+    """The split states of a pair are summed in slot order with the merging CTA's own state at its
+    slot position, so the two ways of choosing the merging CTA - the pair's first CTA, or the last
+    one to arrive by ticket (`STREAMATTN_B200_MERGER=ticket`, read when a plan is built) - must
+    give bit-identical outputs, on uniform and on ragged rows."""
+
+    batch, q_heads, kv_heads, dim, kv_len = 4, 16, 2, 64, 16384
+    q = _randn((batch, 1, q_heads, dim), 40, dev)
+    k = _randn((batch, kv_heads, kv_len, dim), 41, dev)
+    v = _randn((batch, kv_heads, kv_len, dim), 42, dev)
+    lens = torch.tensor([16384, 9000, 12345, 4097], dtype=torch.int32, device=dev)
+    outs = {}
+    for form in ("first", "ticket"):
+        if form == "ticket":
+            monkeypatch.setenv("STREAMATTN_B200_MERGER", "ticket")
+        else:
+            monkeypatch.delenv("STREAMATTN_B200_MERGER", raising=False)
+        uniform = sa.ExactDecodePlan.build(q, k, v)
+        ragged = sa.ExactDecodePlan.build(q, k, v, seq_lens=lens)
+        outs[form] = (uniform.run().clone(), ragged.run().clone())
+        assert uniform.device_status() == 0 and ragged.device_status() == 0
+    assert torch.equal(outs["first"][0], outs["ticket"][0])
+    assert torch.equal(outs["first"][1], outs["ticket"][1])
+    _close(outs["first"][0], torch_reference(q, k, v))
